@@ -1,0 +1,272 @@
+"""Saralix on the device against the plain float64 implementation (plain_saralix.py): each mechanism alone, the replay
+schedules (whole; the last tokens one by one; unequal batches one after another, so that slots and pages are used
+again; prompts in pieces down to two tokens beside single tokens), long decoding past windows and page borders, first
+tokens, planted keys at the latent attention kernel, greedy generation through the engine."""
+import numpy as np
+import pytest
+import torch
+
+import plain_saralix as plain
+import tiny_saralix as tiny
+import trace_util as tu
+from plain_lfm3 import load_folder
+
+pytestmark = pytest.mark.gpu
+
+COS = {"float32": 0.999999, "bfloat16": 0.99}
+LENGTHS = [1, 2, 7, 16, 23, 40, 70, 5, 13, 33, 64, 65, 131]
+
+
+def requests_for(name, lengths=LENGTHS):
+    return {f"r{i}": tiny.prompt(name, n, salt=i) for i, n in enumerate(lengths)}
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("saralix_models")
+    made = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in made:
+            made[(name, dtype)] = tiny.make_folder(root, name, dtype)
+        return made[(name, dtype)]
+    return get
+
+
+@pytest.fixture(scope="module")
+def replayers(folders):
+    from xpu_serve_b200.engine.model import load_model
+    from xpu_serve_b200.engine.replay import Replayer
+    made = {}
+
+    def get(name, dtype, max_tokens=1024):
+        key = (name, dtype, max_tokens)
+        if key not in made:
+            made[key] = Replayer(load_model(folders(name, dtype), dtype=dtype), max_tokens, None)
+        return made[key]
+    return get
+
+
+_REFS = {}
+CLOSE_CALL = {"float32": 1e-5, "bfloat16": 0.04}
+
+
+def reference(folder, name, requests, dtype="float32"):
+    """{(request, position): float64 logits}, memoised per folder and request. A token whose choice of experts is a
+    close call at this precision (the gap to the first expert left out is under CLOSE_CALL of the largest router logit)
+    may choose otherwise on the device, and every later position of its sequence sees that: those are left out."""
+    cfg, W = load_folder(folder)
+    out = {}
+    for rid, toks in requests.items():
+        key = (folder, tuple(toks))
+        if key not in _REFS:
+            margins = np.full(len(toks), np.inf)
+            _REFS[key] = (plain.forward(cfg, W, toks, margins=margins), margins)
+        logits, margins = _REFS[key]
+        close = np.nonzero(margins < CLOSE_CALL[dtype])[0]
+        for p in range(len(toks) if close.size == 0 else int(close[0])):
+            out[(rid, p)] = logits[p]
+    return out
+
+
+def check(name, dtype, steps, requests, replayers, folders, max_tokens=1024):
+    rp = replayers(name, dtype, max_tokens)
+    got = tu.collect(steps, tu.run_in_process(rp, steps), tiny.CONFIGS[name]["vocab"])
+    ref = reference(folders(name, dtype), name, requests, dtype)
+    ref = {k: v for k, v in ref.items() if k in got}
+    assert len(ref) >= len(got) // 3, "too many of the test's own tokens are close calls of a router; pick other prompts"
+    gap, where, cos = tu.worst_gap({k: v for k, v in got.items() if k in ref}, ref)
+    tol = tiny.upper_limit(name, dtype)
+    print(f"GAP saralix {name} {dtype} steps={len(steps)} gap={gap:.3e} at {where} cos={cos:.7f} tol={tol:.1e}")
+    assert gap <= tol, f"{name} {dtype}: gap {gap:.3e} at {where}"
+    assert cos >= COS[dtype], f"{name} {dtype}: cosine {cos}"
+    rp.cache.check()
+    assert rp.cache.slots.held_count == 0 and rp.cache.tokens_held() == 0
+    return got
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["gated", "windowed", "recurrent", "dense", "routed"])
+def test_one_mechanism_alone(name, dtype, replayers, folders):
+    """Single-layer models (the mixers without any feed-forward): a whole prompt, then the same with its tail token by
+    token, then two unequal requests together."""
+    reqs = requests_for(name, [1, 2, 11, 37, 90])
+    check(name, dtype, tu.whole_trace(reqs), reqs, replayers, folders)
+    check(name, dtype, tu.tail_trace(reqs, tail=20), reqs, replayers, folders)
+    check(name, dtype, tu.batch_trace(reqs, 3), reqs, replayers, folders)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["M", "N"])
+def test_whole(name, dtype, replayers, folders):
+    reqs = requests_for(name)
+    check(name, dtype, tu.whole_trace(reqs), reqs, replayers, folders)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["M", "N"])
+def test_prefill_then_token_by_token(name, dtype, replayers, folders):
+    reqs = requests_for(name)
+    check(name, dtype, tu.tail_trace(reqs, tail=32), reqs, replayers, folders)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("batch", [3, 5, 13])
+@pytest.mark.parametrize("name", ["M", "N"])
+def test_unequal_batches_one_after_another(name, batch, dtype, replayers, folders):
+    """Batches of unequal requests against each alone (the reference runs each alone); a later batch takes the slots
+    and pages that the one before gave back, in a cache that holds little more than one batch."""
+    reqs = requests_for(name)
+    check(name, dtype, tu.batch_trace(reqs, batch), reqs, replayers, folders, max_tokens=640)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("pieces", [(2, 3, 64, 5), (7, 64, 65, 129, 3, 16, 40), (130, 2)])
+@pytest.mark.parametrize("name", ["M", "N"])
+def test_prompts_in_pieces(name, pieces, dtype, replayers, folders):
+    """Pieces of several sizes, down to two tokens, at page borders and across windows, in steps that mix a later piece
+    of one request with single tokens of others."""
+    reqs = requests_for(name, [131, 2, 70, 23, 140, 64, 9])
+    check(name, dtype, tu.pieces_trace(reqs, 4, pieces=pieces), reqs, replayers, folders)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["M", "N"])
+def test_long_decoding(name, dtype, replayers, folders):
+    """A short prompt and 200 tokens one by one: past both windows, over three page borders, with the recurrent state
+    carried through every step; beside it a second request that ends early."""
+    reqs = {"long": tiny.prompt(name, 204, salt=3), "short": tiny.prompt(name, 30, salt=4)}
+    check(name, dtype, tu.batch_trace(reqs, 2, prompt_frac=0.02), reqs, replayers, folders)
+
+
+def test_a_lost_part_is_caught(replayers, folders, monkeypatch):
+    """The bounds see a sink that is left out, a window one token too long, and a state that is not carried."""
+    from xpu_serve_b200.ops import lib as ops
+    from xpu_serve_b200.parts.latent_attention import LatentAttentionMixer
+    reqs = requests_for("M", [40, 70])
+    steps = tu.tail_trace(reqs, tail=10)
+    real = ops.latent_attention_generic
+
+    def no_sink(q_lat, q_rot, pool, table, seqs, pos, gate, sink, out, page_size, scale, window):
+        return real(q_lat, q_rot, pool, table, seqs, pos, gate, None, out, page_size, scale, window)
+
+    def wide_window(q_lat, q_rot, pool, table, seqs, pos, gate, sink, out, page_size, scale, window):
+        return real(q_lat, q_rot, pool, table, seqs, pos, gate, sink, out, page_size, scale, window + 1 if window else 0)
+
+    for fault in (no_sink, wide_window):
+        monkeypatch.setattr(ops, "latent_attention_generic", fault)
+        monkeypatch.setattr(LatentAttentionMixer, "fast_path", lambda self, step: False, raising=False)
+        with pytest.raises(AssertionError):
+            check("M", "bfloat16", steps, reqs, replayers, folders)
+        monkeypatch.undo()
+    rp = replayers("M", "bfloat16")
+    monkeypatch.setattr(rp.cache.groups[[i for i, g in enumerate(rp.cache.groups) if not hasattr(g, "pages")][-1]], "zero",
+                        lambda slots: None)
+    check("M", "bfloat16", steps, reqs, replayers, folders)             # leaves states behind in the slots
+    with pytest.raises(AssertionError):
+        check("M", "bfloat16", steps, reqs, replayers, folders)         # ... which the same slots now start from
+
+
+# ------------------------------------------------------------------------------ the attention kernel with planted keys
+def plain_latent_attention(q_lat, q_rot, rows, pos, scale, window, sink, gate):
+    """Float64 attention of one query at position `pos` over cache rows [n, R + Dr]: returns [H, R]."""
+    H, R = q_lat.shape
+    out = np.zeros((H, R))
+    lo = max(0, pos - window + 1) if window > 0 else 0
+    for h in range(H):
+        s = np.array([scale * (q_lat[h] @ rows[j, :R] + q_rot[h] @ rows[j, R:]) for j in range(lo, pos + 1)])
+        top = max(s.max(), sink[h]) if sink is not None else s.max()
+        e = np.exp(s - top)
+        den = e.sum() + (np.exp(sink[h] - top) if sink is not None else 0.0)
+        out[h] = (e / den) @ rows[lo:pos + 1, :R]
+        if gate is not None:
+            out[h] *= 1.0 / (1.0 + np.exp(-gate[h]))
+    return out
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window,sink,gate", [(0, False, True), (37, True, False), (64, True, True), (1, True, False)])
+def test_latent_attention_kernel_with_planted_keys(dtype, window, sink, gate):
+    """Queries of several sequences in one launch (a prompt piece and single tokens), pages in a shuffled order. One key
+    far back, one at a page's last place, one just inside and one just outside the window are made to dominate (their
+    row is the query's direction, scaled), so leaving one out or letting one in changes the result by far more than
+    the bound."""
+    from xpu_serve_b200.ops import lib as ops
+    torch.manual_seed(5)
+    H, R, Dr, page = 3, 40, 8, 64
+    lens = [300, 129, 64, 1]                    # keys of each sequence after the step
+    q_lens = [5, 1, 1, 1]                       # the step's tokens: a piece of 5 and three single tokens
+    n_pages = sum(-(-n // page) for n in lens)
+    order = torch.randperm(n_pages + 3)
+    pool = torch.zeros(n_pages + 4, 1, 1, page, R + Dr, dtype=dtype, device="cuda")
+    table = torch.full((len(lens), 5), -1, dtype=torch.int32)
+    rows_of, at = [], 0
+    for s, n in enumerate(lens):
+        rows = torch.randn(n, R + Dr) * 0.3
+        for p in range(-(-n // page)):
+            table[s, p] = int(order[at]); at += 1
+        rows_of.append(rows)
+    T = sum(q_lens)
+    q_lat = torch.randn(T, H, R) * 0.3
+    q_rot = torch.randn(T, H, Dr) * 0.3
+    positions, seq_of = [], []
+    for s, (n, q) in enumerate(zip(lens, q_lens)):
+        positions += list(range(n - q, n)); seq_of += [s] * q
+    # plant: for the last token of sequence 0 (position 299) and the token of sequence 1 (position 128)
+    for s, t in ((0, 4), (1, 5)):
+        pos = positions[t]
+        for j in {3, 63, 64, pos - window + 1 if window else 7, pos - window if window else 9} - {-1}:
+            if 0 <= j <= pos:
+                direction = torch.cat([q_lat[t, 1], q_rot[t, 1]])
+                rows_of[s][j] = direction / direction.norm() * 6.0
+    for s, rows in enumerate(rows_of):
+        r = rows.to(dtype)
+        rows_of[s] = r.double().numpy()
+        for j in range(r.shape[0]):
+            pool[int(table[s, j // page]), 0, 0, j % page] = r[j].cuda()
+    q_lat_d, q_rot_d = q_lat.to(dtype).cuda(), q_rot.to(dtype).cuda()
+    gate_t = (torch.randn(T, H) * 2).to(dtype).cuda() if gate else None
+    sink_t = (torch.randn(H) * 2).cuda() if sink else None
+    out = torch.empty(T, H, R, dtype=dtype, device="cuda")
+    dev = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    ops.latent_attention_generic(q_lat_d, q_rot_d, pool, table.cuda(), dev(seq_of), dev(positions), gate_t, sink_t, out,
+                                 page, 0.9, window)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    for t in range(T):
+        ref = plain_latent_attention(q_lat_d[t].double().cpu().numpy(), q_rot_d[t].double().cpu().numpy(), rows_of[seq_of[t]],
+                                     positions[t], 0.9, window, sink_t.double().cpu().numpy() if sink else None,
+                                     gate_t[t].double().cpu().numpy() if gate else None)
+        gap = np.abs(out[t].double().cpu().numpy() - ref).max() / max(np.abs(ref).max(), 1e-3)
+        assert gap < tol, (t, positions[t], gap)
+
+
+# --------------------------------------------------------------------------------------------------------- generation
+def plain_greedy(cfg, W, prompt, n):
+    seq, out, margins = list(prompt), [], []
+    for _ in range(n):
+        logits = plain.forward(cfg, W, seq)[-1]
+        order = np.argsort(-logits)
+        margins.append(float(logits[order[0]] - logits[order[1]]) / float(np.abs(logits).max()))
+        out.append(int(order[0]))
+        seq.append(out[-1])
+    return out, margins
+
+
+@pytest.mark.parametrize("chunk", [None, 16])
+def test_greedy_generation_through_the_engine(folders, chunk):
+    """The framework's own entry point and scheduler: three unequal prompts as one batch (with `chunk`, prompts in
+    pieces of 16 tokens), greedy, against the plain implementation run token by token."""
+    from xpu_serve_b200 import GenerateRequest, SamplingParams
+    from xpu_serve_b200.engine.engine import Engine
+    folder = folders("M", "float32")
+    cfg, W = load_folder(folder)
+    kw = {} if chunk is None else {"prefill_chunk": chunk}
+    engine = Engine(folder, precision="f32", ctx=256, max_batch=8, **kw)
+    prompts = [tiny.prompt("M", n, salt=i) for i, n in enumerate((3, 41, 18))]
+    res = engine.generate([GenerateRequest(p, SamplingParams(temperature=0.0), 9, []) for p in prompts])
+    for p, r in zip(prompts, res):
+        want, margins = plain_greedy(cfg, W, p, 9)
+        assert min(margins) > 1e-4, "the test's own tokens are near ties; pick another prompt"
+        assert r.finish == "length" and r.tokens == want
+    engine.stepper.cache.check()
+    assert engine.stepper.cache.slots.held_count == 0

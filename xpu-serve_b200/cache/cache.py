@@ -10,7 +10,7 @@ row per slot. Each group owns its storage. A slot's length is advanced only by
 available (the reference leaves a failed step's state as it was,
 src/backend/cpu_ref/cpu_backend.cpp:157-177).
 
-Storage of a key/value call: [pages, 2 (keys, values), kv_heads, page_size, head_dim].
+Storage of a key/value call: [pages, planes (keys, values; one for a latent), kv_heads, page_size, head_dim].
 Storage of a state call:     [max_slots, *shape].
 """
 from __future__ import annotations
@@ -50,7 +50,7 @@ class KVGroup:
         # one page more than the pool hands out: padding rows of a fixed-size batch write there
         self.dummy_page = n_pages
         self.storage: Dict[Tuple[int, int], torch.Tensor] = {
-            c: torch.zeros((n_pages + 1, 2, need.kv_heads, page_size, need.head_dim),
+            c: torch.zeros((n_pages + 1, need.planes, need.kv_heads, page_size, need.head_dim),
                            dtype=dtype, device=device) for c in calls}
 
     def _first_needed_page(self, start: int) -> int:

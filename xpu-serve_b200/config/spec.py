@@ -82,12 +82,116 @@ class SwiGLUSpec:
 
 
 @dataclass(frozen=True)
+class RopeScalingSpec:
+    """Rotation frequencies stretched for sequences longer than those a model was trained on ("YaRN": pairs that
+    turn more than `fast` times over `original` positions keep their frequency, pairs that turn fewer than `slow`
+    times are divided by `factor`, with a linear ramp over the pair index between; cos and sin are multiplied by
+    `mscale_k` ln(factor) + 1)."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+    mscale_k: float = 0.1
+
+
+@dataclass(frozen=True)
+class ScaledRopeSpec:
+    """A rotate-half rotation of the first `dims` channels of a vector of `head_dim` channels: pair i couples
+    channels i and i + dims/2 (not i + head_dim/2) and turns by pos * theta^(-2i/dims), scaled as `scaling` says
+    (None: as is). The table it gives has head_dim/2 entries a position when dims == head_dim, which the kernels
+    that know one pairing read; the mixers that use it ask for dims == head_dim."""
+    head_dim: int
+    theta: float
+    dims: int
+    scaling: Optional[RopeScalingSpec] = None
+    kind: str = "rope_scaled"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose keys and values of all heads are products of one cached latent vector per position
+    (`kv_rank` numbers, unit RMS times a weight) and of one rotated key part (`rot_dim` numbers) that the heads
+    share. A query head has `dim` unrotated and `rot_dim` rotated channels; a value head `vdim`.
+    window 0: every earlier key; W > 0: keys with pos - j < W. `sink`: a learned number per head joins the softmax's
+    denominator. `head_gate`: o[t, h, :] *= sigmoid((x Wg^T)[t, h])."""
+    hidden: int
+    heads: int
+    dim: int
+    rot_dim: int
+    vdim: int
+    kv_rank: int
+    scale: float
+    eps: float               # of the latent's unit-RMS norm
+    position: Optional[ScaledRopeSpec]
+    window: int = 0
+    sink: bool = False
+    head_gate: bool = False
+    names: Dict[str, str] = field(default_factory=lambda: {
+        "q": "mix.q", "down": "mix.dkv", "latent_norm": "mix.dkv.norm", "up_k": "mix.uk", "up_v": "mix.uv",
+        "gate": "mix.g", "sink": "mix.sink", "o": "mix.o"})
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class Mamba2Spec:
+    """A selective state-space recurrence per head (state [state, vdim], float32) behind a causal depthwise
+    convolution with silu over [x | B | C]; the output is gated by silu(z) and then unit-RMS normed in
+    `norm_groups` equal parts. in_proj's rows: [z: inner | x: inner | B: groups*state | C: groups*state | dt: heads],
+    inner = heads * vdim; head h reads the B and C of group h // (heads / groups)."""
+    hidden: int
+    heads: int
+    vdim: int
+    state: int
+    groups: int
+    taps: int
+    norm_groups: int
+    eps: float
+    names: Dict[str, str] = field(default_factory=lambda: {
+        "in": "mix.in", "conv": "mix.conv", "conv_bias": "mix.conv.b", "dt_bias": "mix.dt_bias", "a_log": "mix.A_log",
+        "d": "mix.D", "norm": "mix.norm", "out": "mix.o"})
+    kind: str = "mamba2"
+
+    @property
+    def inner(self) -> int:
+        return self.heads * self.vdim
+
+    @property
+    def conv_channels(self) -> int:
+        return self.inner + 2 * self.groups * self.state
+
+
+@dataclass(frozen=True)
+class ClampedGLUSpec:
+    """down(g * sigmoid(alpha g) * (u + up_shift)) with g = min(gate x, limit), u = clamp(up x, -limit, limit)."""
+    hidden: int
+    intermediate: int
+    limit: float
+    alpha: float = 1.702
+    up_shift: float = 1.0
+    names: Dict[str, str] = field(default_factory=lambda: {"gate": "mlp.gate", "up": "mlp.up", "down": "mlp.down"})
+    kind: str = "clamped_glu"
+
+
+@dataclass(frozen=True)
+class RoutedExpertsSpec:
+    """`experts` SwiGLU feed-forwards without biases, of which a token uses the `top` with the largest router
+    logits (float32), weighted by the softmax over those logits alone."""
+    hidden: int
+    intermediate: int
+    experts: int
+    top: int
+    names: Dict[str, str] = field(default_factory=lambda: {
+        "router": "mlp.router", "gate": "mlp.e{e}.gate", "up": "mlp.e{e}.up", "down": "mlp.e{e}.down"})
+    kind: str = "routed_experts"
+
+
+@dataclass(frozen=True)
 class NormSpec:
     """RMSNorm over the last dimension, x * (mean(x^2) + eps)^(-1/2) * w, no +1 offset
     (src/graph/graph.h:57, src/backend/cpu_ref/ops.cpp:260-281)."""
     width: int
     eps: float
-    kind: str = "rmsnorm"
+    kind: str = "rmsnorm"    # "layernorm": (x - mean) * (variance + eps)^(-1/2) * w, no bias (parts/layernorm.py)
 
 
 @dataclass(frozen=True)
@@ -97,7 +201,7 @@ class LayerSpec:
     the identity and their tensors are not read."""
     prefix: str              # tensor-name prefix under the model prefix, e.g. "layers.3."
     mixer: object            # a spec with a `kind`
-    ffn: object              # a spec with a `kind`
+    ffn: object              # a spec with a `kind`, or None: the layer has no feed-forward (and no norms for one)
     norm: NormSpec
     sandwich: bool
     names: Dict[str, str] = field(default_factory=lambda: {
@@ -130,6 +234,7 @@ class ModelSpec:
     embed_scale: float = 1.0  # the embedding rows are multiplied by it (1: as stored, LFM3's)
     logit_cap: float = 0.0    # > 0: logits = cap * tanh(logits / cap) (0: none, LFM3's)
     prefixes: Tuple[str, ...] = ("model.",)   # tried in turn for "<prefix>embed_tokens.weight"
+    ignorable: Tuple[str, ...] = ()           # regular expressions: tensors of a folder that match are neither needed nor refused
     names: Dict[str, str] = field(default_factory=lambda: {
         "embed": "embed_tokens.weight", "final_norm": "embedding_norm.weight",
         "head": "lm_head.weight"})   # "head" is looked up without the model prefix

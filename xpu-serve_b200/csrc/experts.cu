@@ -1,0 +1,291 @@
+// Routed experts (a mixture of small gated feed-forwards) and the clamped gated unit's activation.
+//
+// A step's tokens each choose `top` of E experts. Four kernels, none of which needs the host to know a count:
+//   route    per token: the `top` largest float32 router logits (ties: the lower index), softmax over them alone
+//   plan     one CTA: rows (token, choice) counted per expert, each given a place in an order sorted by expert, and
+//            the list of row tiles (expert, first row, rows) that the products walk; its length stays on the device
+//   product  out[row] = W[expert of row] x[source of row], tile by tile of the plan; the grid is sized by the most
+//            tiles that T * top rows over E experts can make, surplus CTAs leave at once
+//            (first product: rows gathered from the tokens, epilogue silu(gate) * up; second: rows in place)
+//   combine  y[t] = sum_k weight[t, k] * out[place of (t, k)], in float32, in the order of k
+// The generic product sums each output's K terms in an order that depends on K alone, as gemm_generic.cu does.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kMaxTop = 16;
+
+__device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// ---------------------------------------------------------------------------------------------- clamped gated unit
+// out[t, f] = g * sigmoid(alpha g) * (u + shift), g = min(gate, limit), u = clamp(up, -limit, limit); a row of gu is
+// [F gate | F up].
+template <typename T>
+__global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total, int F, int64_t ld,
+                                   float limit, float alpha, float shift) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / F;
+        const int f = (int)(i - t * F);
+        const float g = fminf(to_f32(gu[t * ld + f]), limit);
+        const float u = fminf(fmaxf(to_f32(gu[t * ld + F + f]), -limit), limit);
+        out[i] = from_f32<T>(g * sigmoid_f(alpha * g) * (u + shift));
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------ route
+__global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int top, int32_t* __restrict__ ids,
+                                 float* __restrict__ wts) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= T) return;
+    const float* z = logits + (int64_t)t * E;
+    int chosen[kMaxTop];
+    float val[kMaxTop];
+    for (int k = 0; k < top; ++k) {
+        int best = -1;
+        float bv = 0.0f;
+        for (int e = 0; e < E; ++e) {
+            bool taken = false;
+            for (int j = 0; j < k; ++j) taken |= chosen[j] == e;
+            if (taken) continue;
+            const float v = z[e];
+            if (best < 0 || v > bv) {
+                best = e;
+                bv = v;
+            }
+        }
+        chosen[k] = best;
+        val[k] = bv;
+    }
+    float sum = 0.0f;
+    const float largest = val[0];
+    for (int k = 0; k < top; ++k) {
+        val[k] = expf(val[k] - largest);
+        sum += val[k];
+    }
+    for (int k = 0; k < top; ++k) {
+        ids[(int64_t)t * top + k] = chosen[k];
+        wts[(int64_t)t * top + k] = val[k] / sum;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------------------- plan
+// meta: [0] number of tiles; then per tile 3 words (expert, first row, rows) from meta[4] on.
+__global__ void moe_plan_kernel(const int32_t* __restrict__ ids, int n, int E, int tile_rows, int32_t* __restrict__ place,
+                                int32_t* __restrict__ source, int32_t* __restrict__ meta) {
+    extern __shared__ int32_t sm[];      // count[E], first[E], next[E]
+    int32_t* count = sm;
+    int32_t* first = sm + E;
+    int32_t* next = sm + 2 * E;
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0, tiles = 0;
+        for (int e = 0; e < E; ++e) {
+            first[e] = at;
+            next[e] = at;
+            for (int r = 0; r < count[e]; r += tile_rows) {
+                int32_t* m = meta + 4 + 3 * tiles;
+                m[0] = e;
+                m[1] = at + r;
+                m[2] = min(tile_rows, count[e] - r);
+                ++tiles;
+            }
+            at += count[e];
+        }
+        meta[0] = tiles;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int p = atomicAdd(&next[ids[i]], 1);
+        place[i] = p;
+        source[p] = i;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------- product
+// out[row, :] = W[e] . x[src(row)] for the rows of one tile; W is [E, N(,2), K] stacked. GLU: W[e] is [2 N, K], gate
+// rows first, and out = silu(gate) * up. src(row) = source[row] / top when `source` is given (rows gathered from the
+// tokens), else row.
+constexpr int TM = 64, TN = 64, TK = 32;
+
+template <typename TX, typename TO, bool GLU>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const TX* __restrict__ x, int64_t ldx, const TX* __restrict__ w, TO* __restrict__ out, int64_t ldo,
+                const int32_t* __restrict__ source, int top, const int32_t* __restrict__ meta, int N, int K) {
+    __shared__ float xs[TK][TM + 1];
+    __shared__ float ws[GLU ? 2 : 1][TK][TN + 1];
+    __shared__ int64_t src_row[TM];
+    pdl_launch_dependents();
+    pdl_wait();
+    if ((int)blockIdx.y >= meta[0]) return;
+    const int32_t* mt = meta + 4 + 3 * blockIdx.y;
+    const int e = mt[0], row0 = mt[1], rows = mt[2];
+    const int n0 = blockIdx.x * TN;
+    const TX* we = w + (int64_t)e * (GLU ? 2 : 1) * N * K;
+    if (threadIdx.x < TM) {
+        const int r = row0 + threadIdx.x;
+        src_row[threadIdx.x] = threadIdx.x < rows ? (source != nullptr ? source[r] / top : r) : -1;
+    }
+    __syncthreads();
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[GLU ? 2 : 1][4][4];
+#pragma unroll
+    for (int g = 0; g < (GLU ? 2 : 1); ++g)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) acc[g][i][j] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += TK) {
+        for (int idx = threadIdx.x; idx < TM * TK; idx += 256) {
+            const int r = idx >> 5, k = idx & 31;
+            const int gn = n0 + r, gk = k0 + k;
+            const int64_t sr = src_row[r];
+            xs[k][r] = (sr >= 0 && gk < K) ? to_f32(x[sr * ldx + gk]) : 0.0f;
+            ws[0][k][r] = (gn < N && gk < K) ? to_f32(we[(int64_t)gn * K + gk]) : 0.0f;
+            if (GLU) ws[GLU ? 1 : 0][k][r] = (gn < N && gk < K) ? to_f32(we[(int64_t)(N + gn) * K + gk]) : 0.0f;
+        }
+        __syncthreads();
+        float part[GLU ? 2 : 1][4][4];
+#pragma unroll
+        for (int g = 0; g < (GLU ? 2 : 1); ++g)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) part[g][i][j] = 0.0f;
+#pragma unroll
+        for (int k = 0; k < TK; ++k) {
+            float a[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] = xs[k][ty * 4 + i];
+#pragma unroll
+            for (int g = 0; g < (GLU ? 2 : 1); ++g) {
+                float b[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) b[j] = ws[g][k][tx * 4 + j];
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) part[g][i][j] = fmaf(a[i], b[j], part[g][i][j]);
+            }
+        }
+#pragma unroll
+        for (int g = 0; g < (GLU ? 2 : 1); ++g)
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[g][i][j] += part[g][i][j];
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = ty * 4 + i;
+        if (r >= rows) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int gn = n0 + tx * 4 + j;
+            if (gn >= N) continue;
+            float v = acc[0][i][j];
+            if (GLU) {
+                // the gate and the up product are rounded to the activation type first, as two separate products' would be
+                const float g = to_f32(from_f32<TO>(v)), u = to_f32(from_f32<TO>(acc[GLU ? 1 : 0][i][j]));
+                v = g * sigmoid_f(g) * u;
+            }
+            out[(int64_t)(row0 + r) * ldo + gn] = from_f32<TO>(v);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------- combine
+template <typename TI, typename TO>
+__global__ void moe_combine_kernel(const TI* __restrict__ rows_out, const int32_t* __restrict__ place,
+                                   const float* __restrict__ wts, TO* __restrict__ y, int H, int top) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        float v = 0.0f;
+        for (int k = 0; k < top; ++k)
+            v = fmaf(wts[(int64_t)t * top + k], to_f32(rows_out[(int64_t)place[(int64_t)t * top + k] * H + c]), v);
+        y[(int64_t)t * H + c] = from_f32<TO>(v);
+    }
+}
+
+}  // namespace
+
+XS_API int xs_clamped_glu(const void* gu, void* out, int dtype, int T, int F, int64_t ld, float limit, float alpha,
+                          float shift, cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(T > 0 && F > 0 && ld >= 2 * (int64_t)F, "clamped_glu: %d rows, %d columns, stride %lld", T, F, (long long)ld);
+    const int64_t total = (int64_t)T * F;
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    XS_DISPATCH_DTYPE(dtype, TT,
+                      xs_launch(clamped_glu_kernel<TT>, dim3(blocks), dim3(256), 0, stream, (const TT*)gu, (TT*)out, total,
+                                F, ld, limit, alpha, shift));
+    XS_LAUNCH_CHECK("clamped_glu");
+    return 0;
+}
+
+XS_API int xs_moe_route(const float* logits, int T, int E, int top, int32_t* ids, float* wts, cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(T > 0 && E > 0 && top > 0 && top <= E && top <= kMaxTop, "moe_route: %d tokens, %d experts, top %d (at most %d)",
+               T, E, top, kMaxTop);
+    xs_launch(moe_route_kernel, dim3(ceil_div_i(T, 128)), dim3(128), 0, stream, logits, T, E, top, ids, wts);
+    XS_LAUNCH_CHECK("moe_route");
+    return 0;
+}
+
+XS_API int xs_moe_tile_rows() { return TM; }
+
+// How many tiles n rows over E experts can make at most: whole tiles, and a partly filled one per expert.
+XS_API int xs_moe_max_tiles(int n, int E) { return n / TM + (n < E ? n : E); }
+
+XS_API int xs_moe_plan(const int32_t* ids, int n, int E, int32_t* place, int32_t* source, int32_t* meta,
+                       cudaStream_t stream) {
+    if (n == 0) return 0;
+    XS_REQUIRE(n > 0 && E > 0 && E <= 4096, "moe_plan: %d rows, %d experts (at most 4096)", n, E);
+    xs_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int32_t), stream, ids, n, E, TM, place, source, meta);
+    XS_LAUNCH_CHECK("moe_plan");
+    return 0;
+}
+
+// x and w share an element type; out is float32 or that type. glu: w is [E, 2 N, K] and out = silu(gate) * up.
+XS_API int xs_moe_gemm(const void* x, int64_t ldx, const void* w, void* out, int64_t ldo, const int32_t* source, int top,
+                       const int32_t* meta, int max_tiles, int N, int K, int glu, int in_dtype, int out_dtype,
+                       cudaStream_t stream) {
+    if (max_tiles == 0) return 0;
+    XS_REQUIRE(max_tiles > 0 && max_tiles <= 65535 && N > 0 && K > 0 && top > 0, "moe_gemm: %d tiles, N %d, K %d", max_tiles, N, K);
+    XS_REQUIRE(in_dtype == out_dtype, "moe_gemm: element types in %d, out %d", in_dtype, out_dtype);
+    const dim3 grid(ceil_div_i(N, TN), max_tiles);
+#define XS_GO(TT)                                                                                                   \
+    do {                                                                                                            \
+        if (glu)                                                                                                    \
+            xs_launch(moe_gemm_kernel<TT, TT, true>, grid, dim3(256), 0, stream, (const TT*)x, ldx, (const TT*)w,   \
+                      (TT*)out, ldo, source, top, meta, N, K);                                                      \
+        else                                                                                                        \
+            xs_launch(moe_gemm_kernel<TT, TT, false>, grid, dim3(256), 0, stream, (const TT*)x, ldx, (const TT*)w,  \
+                      (TT*)out, ldo, source, top, meta, N, K);                                                      \
+    } while (0)
+    XS_DISPATCH_DTYPE(in_dtype, TT, XS_GO(TT));
+#undef XS_GO
+    XS_LAUNCH_CHECK("moe_gemm");
+    return 0;
+}
+
+XS_API int xs_moe_combine(const void* rows_out, const int32_t* place, const float* wts, void* y, int T, int H, int top,
+                          int dtype, cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(T > 0 && H > 0 && top > 0, "moe_combine: %d tokens of %d, top %d", T, H, top);
+    XS_DISPATCH_DTYPE(dtype, TT,
+                      xs_launch(moe_combine_kernel<TT, TT>, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, stream,
+                                (const TT*)rows_out, place, wts, (TT*)y, H, top));
+    XS_LAUNCH_CHECK("moe_combine");
+    return 0;
+}

@@ -114,7 +114,8 @@ class Model:
         # Only when every part of the model says that its prompt code can be captured for any lengths (parts/base.py).
         parts_ok = all(getattr(c, "fixed_shape_ok", False) for layer in spec.layers for c in (
             registry.arrangement_class(layer.kind), registry.mixer_class(layer.mixer.kind),
-            registry.ffn_class(layer.ffn.kind), registry.norm_class(layer.norm.kind)))
+            registry.norm_class(layer.norm.kind),
+            *([registry.ffn_class(layer.ffn.kind)] if layer.ffn is not None else [])))
         parts_ok = parts_ok and getattr(registry.norm_class(spec.final_norm.kind), "fixed_shape_ok", False)
         self.use_prompt_graphs = self.use_graphs and parts_ok and os.environ.get("XS_NO_PROMPT_GRAPHS", "0") != "1"
         self._prompt_graphs: Dict[int, Dict[int, _DecodeGraph]] = {}

@@ -102,6 +102,7 @@ class Runtime:
         if self.many_rows not in ("auto", "library", "tcgen05"):
             raise ValueError("XS_MANY_ROWS_GEMM must be 'auto', 'library' or 'tcgen05'")
         self.fused_from_rows = 512
+        self.batched_library_from = int(os.environ.get("XS_BATCHED_LIBRARY_FROM", "32"))
         ops.load()
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.gemm_scratch = torch.zeros(8 * 1024 * 1024, dtype=torch.uint8, device=self.device)
@@ -204,6 +205,18 @@ class Runtime:
         rows = getattr(x, "x", x).shape[0]
         return (self.fuse_tails and self.tail_conv and rows <= 8 and self.few_rows(x, w) and channels % 16 == 0
                 and channels // 16 <= self.conv_counters.numel() and w.shape[0] == 3 * channels)
+
+    def batched_product(self, x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+        """out[b] = x[b] . w[b]^T for x [B, M, K], w [B, N, K], out [B, M, N] (views with contiguous last dimensions):
+        the per-head products of latent attention. The float32 mode and few rows use this library's kernel (sums in an
+        order that depends on K alone); more rows in bfloat16 go to the vendor's batched product, as the plain products
+        of that size do."""
+        if self.mode == "float32" or x.shape[1] <= self.batched_library_from:
+            ops.gemm_batched(x, w, out)
+        elif out.is_contiguous():
+            torch.bmm(x, w.transpose(1, 2), out=out)
+        else:
+            out.copy_(torch.bmm(x, w.transpose(1, 2)))
 
     def linear(self, x: torch.Tensor, w: torch.Tensor, name: str, bias: Optional[torch.Tensor] = None,
                out_dtype: Optional[torch.dtype] = None, argmax_into: Optional[torch.Tensor] = None) -> torch.Tensor:

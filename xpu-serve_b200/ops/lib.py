@@ -53,6 +53,19 @@ def _signatures(lib) -> None:
         "xs_sample": [P, L, I, I, P, P, P, P, P, P, I, P, P],
         "xs_apply_penalties": [P, L, I, I, P, P, P, P, P, P, P],
         "xs_note_tokens": [P, P, I, I, P, P, I, P],
+        "xs_add_layernorm": [P, P, I, P, P, P, I, P, I, I, F, F, P],
+        "xs_grouped_rmsnorm": [P, P, P, I, I, I, I, F, P],
+        "xs_clamped_glu": [P, P, I, I, I, L, F, F, F, P],
+        "xs_moe_route": [P, I, I, I, P, P, P],
+        "xs_moe_plan": [P, I, I, P, P, P, P],
+        "xs_moe_gemm": [P, L, P, P, L, P, I, P, I, I, I, I, I, I, P],
+        "xs_moe_combine": [P, P, P, P, I, I, I, I, P],
+        "xs_latent_prepare": [P, L, P, L, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, I, P],
+        "xs_latent_attention_generic": [P, L, L, P, P, P, I, P, P, P, L, P, P, L, L, I, I, I, I, I, F, I, I, P],
+        "xs_gemm_batched": [P, L, L, P, L, L, P, L, L, I, I, I, I, I, P],
+        "xs_mamba2_conv": [P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, P],
+        "xs_mamba2_scan": [P, P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
+        "xs_mamba2_scan_chunked": [P, P, L, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
     }
     for name, args in sig.items():
         fn = getattr(lib, name)
@@ -79,6 +92,10 @@ def _signatures(lib) -> None:
     lib.xs_gemm_tc_tile_n.argtypes = [c_int]
     lib.xs_gemm_tc_scratch_bytes.restype = c_int64
     lib.xs_gemm_tc_scratch_bytes.argtypes = [c_int, c_int, c_int]
+    lib.xs_moe_tile_rows.restype = c_int
+    lib.xs_moe_tile_rows.argtypes = []
+    lib.xs_moe_max_tiles.restype = c_int
+    lib.xs_moe_max_tiles.argtypes = [c_int, c_int]
     lib.xs_gemm_small_m_ksplit.restype = c_int
     lib.xs_gemm_small_m_ksplit.argtypes = [c_int, c_int, c_int, c_int]
     lib.xs_gemm_small_m_scratch_bytes.restype = c_int64
@@ -729,3 +746,224 @@ def note_tokens(tokens: torch.Tensor, rows_of_token: torch.Tensor, seen: torch.T
     V = seen.shape[1]
     _check(load().xs_note_tokens(tokens.data_ptr(), rows_of_token.data_ptr(), tokens.numel(), V, seen.data_ptr(),
                                  gen_count.data_ptr(), 1 if generated else 0, _stream()))
+
+
+# ------------------------------------------------ layer norm, grouped unit norm, clamped gated unit
+def add_layernorm(h: torch.Tensor, m: Optional[torch.Tensor], post_w: Optional[torch.Tensor],
+                  w: Optional[torch.Tensor], y: Optional[torch.Tensor], rows: Optional[torch.Tensor], eps: float,
+                  eps_post: Optional[float] = None) -> None:
+    """h += LN(m, post_w) (m alone without post_w), if m; y = LN(h, w) (if w), over `rows` of h when given; LN is the
+    layer norm with a weight and no bias."""
+    _need(h, "h", torch.float32)
+    H = h.shape[-1]
+    n = h.shape[0] if rows is None else rows.numel()
+    if m is not None:
+        _need(m, "m")
+        if m.shape != h.shape:
+            raise KernelError(f"m is {tuple(m.shape)}, h is {tuple(h.shape)}")
+    for v, name in ((post_w, "post_w"), (w, "w")):
+        if v is not None:
+            _need(v, name, torch.float32)
+            if v.numel() != H:
+                raise KernelError(f"{name} has {v.numel()} elements for rows of {H}")
+    if y is not None:
+        _need(y, "y")
+        if y.shape[0] < n or y.shape[-1] != H:
+            raise KernelError(f"y is {tuple(y.shape)} for {n} rows of {H}")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    _check(load().xs_add_layernorm(h.data_ptr(), _ptr(m), F32 if m is None else _code(m), _ptr(post_w), _ptr(w),
+                                   _ptr(y), F32 if y is None else _code(y), _ptr(rows), n, H,
+                                   float(eps if eps_post is None else eps_post), float(eps), _stream()))
+
+
+def grouped_rmsnorm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, groups: int, eps: float) -> None:
+    """y[t, g] = x[t, g] / sqrt(mean(x[t, g]^2) + eps) * w[g] for the `groups` equal parts g of a row; x float32."""
+    _need(x, "x", torch.float32); _need(w, "w", torch.float32); _need(y, "y")
+    if y.shape != x.shape or w.numel() != x.shape[1]:
+        raise KernelError(f"grouped_rmsnorm: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    _check(load().xs_grouped_rmsnorm(x.data_ptr(), w.data_ptr(), y.data_ptr(), _code(y), x.shape[0], x.shape[1],
+                                     int(groups), float(eps), _stream()))
+
+
+def clamped_glu(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, shift: float) -> None:
+    """out = g * sigmoid(alpha g) * (u + shift), g = min(gate, limit), u = clamp(up, -limit, limit); a row of gu is
+    [gate | up]."""
+    _need(out, "out", gu.dtype)
+    if not gu.is_cuda or gu.dim() != 2 or gu.stride(1) != 1:
+        raise KernelError("gate_up must be a CUDA matrix with contiguous rows")
+    T, F = out.shape
+    if gu.shape[0] != T or gu.shape[1] < 2 * F:
+        raise KernelError(f"gate_up is {tuple(gu.shape)} for an output of {tuple(out.shape)}")
+    _check(load().xs_clamped_glu(gu.data_ptr(), out.data_ptr(), _code(gu), T, F, gu.stride(0), float(limit), float(alpha),
+                                 float(shift), _stream()))
+
+
+# ------------------------------------------------------------------------------- routed experts
+def moe_max_tiles(rows: int, experts: int) -> int:
+    """The most row tiles that `rows` rows over `experts` experts can make (what the products' grids are sized by)."""
+    return int(load().xs_moe_max_tiles(rows, experts))
+
+
+def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, wts: torch.Tensor) -> None:
+    """Per row of float32 logits: the `top` largest (ties: the lower index) into ids, their softmax into wts."""
+    _need(logits, "router logits", torch.float32); _need(ids, "ids", torch.int32); _need(wts, "weights", torch.float32)
+    T, E = logits.shape
+    if ids.numel() < T * top or wts.numel() < T * top:
+        raise KernelError(f"moe_route: {T} tokens x top {top} do not fit ids {ids.numel()} / weights {wts.numel()}")
+    _check(load().xs_moe_route(logits.data_ptr(), T, E, int(top), ids.data_ptr(), wts.data_ptr(), _stream()))
+
+
+def moe_plan(ids: torch.Tensor, experts: int, place: torch.Tensor, source: torch.Tensor, meta: torch.Tensor) -> None:
+    """Sorts the rows (token, choice) by expert: place[row] = its place in that order, source[place] = row, and meta =
+    [tiles, -, -, -, (expert, first place, rows) per tile]."""
+    n = ids.numel()
+    for t, name in ((ids, "ids"), (place, "place"), (source, "source"), (meta, "meta")):
+        _need(t, name, torch.int32)
+    if place.numel() < n or source.numel() < n or meta.numel() < 4 + 3 * moe_max_tiles(n, experts):
+        raise KernelError("moe_plan: an output is too small")
+    _check(load().xs_moe_plan(ids.data_ptr(), n, int(experts), place.data_ptr(), source.data_ptr(), meta.data_ptr(), _stream()))
+
+
+def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch.Tensor, rows: int, source: Optional[torch.Tensor],
+             top: int, glu: bool) -> None:
+    """out[place] = w[expert of place] . x[source[place] // top] (x[place] without `source`) for the `rows` sorted
+    places of a plan. w: [experts, N, K], or [experts, 2 N, K] with `glu` (gate rows first; out = silu(gate) * up)."""
+    for t, name in ((x, "x"), (out, "out")):
+        if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
+            raise KernelError(f"moe_gemm: {name} must be a CUDA matrix with contiguous rows")
+    _need(w, "expert weights", x.dtype)
+    E, N, K = w.shape
+    if glu:
+        N //= 2
+    if x.shape[1] != K or out.shape[1] != N or out.shape[0] < rows or out.dtype != x.dtype:
+        raise KernelError(f"moe_gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    _check(load().xs_moe_gemm(x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), _ptr(source), int(top),
+                              meta.data_ptr(), moe_max_tiles(rows, E), N, K, 1 if glu else 0, _code(x), _code(out), _stream()))
+
+
+def moe_combine(rows_out: torch.Tensor, place: torch.Tensor, wts: torch.Tensor, y: torch.Tensor, top: int) -> None:
+    """y[t] = sum_k wts[t, k] * rows_out[place[t, k]], summed in float32 in the order of k."""
+    _need(rows_out, "expert outputs", y.dtype); _need(y, "y")
+    T, H = y.shape
+    _check(load().xs_moe_combine(rows_out.data_ptr(), place.data_ptr(), wts.data_ptr(), y.data_ptr(), T, H, int(top),
+                                 _code(y), _stream()))
+
+
+# ----------------------------------------------------------------------------- latent attention
+def latent_prepare(down: torch.Tensor, q: torch.Tensor, norm_w: torch.Tensor, table: Optional[torch.Tensor],
+                   positions: torch.Tensor, seq_of_token: torch.Tensor, page_table: torch.Tensor, pool: torch.Tensor,
+                   q_rot: torch.Tensor, heads: int, dim: int, rot_dim: int, rank: int, dims: int, page_size: int,
+                   eps: float, write_kv: bool = True) -> None:
+    """From the down-projection [T, rank + rot_dim] and the queries [T, heads * (dim + rot_dim)]: the cache row
+    [unit-RMS(down[:rank]) * norm_w | rotated down[rank:]] at each token's position, and every head's rotated query part
+    into q_rot [T, heads, rot_dim]. table: [positions, dims / 2, 2] (cos, sin)."""
+    _need(q_rot, "q_rot", q.dtype); _need(pool, "cache", q.dtype); _need(norm_w, "latent norm weight", torch.float32)
+    _need(page_table, "page table", torch.int32)
+    T = q.shape[0]
+    if down.stride(1) != 1 or q.stride(1) != 1 or down.shape[1] < rank + rot_dim or q.shape[1] < heads * (dim + rot_dim):
+        raise KernelError(f"latent_prepare: down {tuple(down.shape)}, q {tuple(q.shape)}")
+    if tuple(pool.shape[1:]) != (1, 1, page_size, rank + rot_dim):
+        raise KernelError(f"cache is {tuple(pool.shape)}, expected [*, 1, 1, {page_size}, {rank + rot_dim}]")
+    if table is not None:
+        _need(table, "rotation table", torch.float32)
+        if tuple(table.shape[1:]) != (dims // 2, 2):
+            raise KernelError(f"rotation table is {tuple(table.shape)}, expected [*, {dims // 2}, 2]")
+    _check(load().xs_latent_prepare(down.data_ptr(), down.stride(0), q.data_ptr(), q.stride(0), norm_w.data_ptr(),
+                                    _ptr(table), positions.data_ptr(), seq_of_token.data_ptr(), page_table.data_ptr(),
+                                    page_table.shape[1], pool.data_ptr(), q_rot.data_ptr(), T, heads, dim, rot_dim, rank,
+                                    dims if table is not None else 0, page_size, float(eps), 1 if write_kv else 0, _code(q),
+                                    _stream()))
+
+
+def latent_attention_generic(q_lat: torch.Tensor, q_rot: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor,
+                             seq_of_token: torch.Tensor, positions: torch.Tensor, gate: Optional[torch.Tensor],
+                             sink: Optional[torch.Tensor], out: torch.Tensor, page_size: int, scale: float,
+                             window: int) -> None:
+    """q_lat, out: [T, heads, rank] views (any token and head strides, contiguous channels); q_rot [T, heads, rot_dim]."""
+    T, H, R = q_lat.shape
+    Dr = q_rot.shape[2]
+    _need(q_rot, "q_rot", q_lat.dtype); _need(pool, "cache", q_lat.dtype); _need(page_table, "page table", torch.int32)
+    if q_lat.stride(2) != 1 or out.stride(2) != 1 or tuple(out.shape) != (T, H, R) or out.dtype != q_lat.dtype:
+        raise KernelError(f"latent attention: q {tuple(q_lat.shape)}, out {tuple(out.shape)}")
+    if tuple(pool.shape[1:]) != (1, 1, page_size, R + Dr):
+        raise KernelError(f"cache is {tuple(pool.shape)}, expected [*, 1, 1, {page_size}, {R + Dr}]")
+    ld_gate = 0
+    if gate is not None:
+        if gate.dtype != q_lat.dtype or gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] < H:
+            raise KernelError(f"gate is {tuple(gate.shape)} {gate.dtype} for {T} tokens of {H} heads")
+        ld_gate = gate.stride(0)
+    if sink is not None:
+        _need(sink, "sink", torch.float32)
+    _check(load().xs_latent_attention_generic(
+        q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_rot.data_ptr(), pool.data_ptr(), page_table.data_ptr(),
+        page_table.shape[1], seq_of_token.data_ptr(), positions.data_ptr(), _ptr(gate), ld_gate, _ptr(sink), out.data_ptr(),
+        out.stride(0), out.stride(1), T, H, R, Dr, page_size, float(scale), int(window), _code(q_lat), _stream()))
+
+
+def gemm_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:
+    """out[b] = x[b] . w[b]^T for [batch, M, K], [batch, N, K] and [batch, M, N] views with contiguous last dimensions
+    and any row and batch strides."""
+    B, M, K = x.shape
+    N = w.shape[1]
+    if w.shape != (B, N, K) or out.shape != (B, M, N) or x.dtype != w.dtype or out.dtype != x.dtype:
+        raise KernelError(f"gemm_batched: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    for t in (x, w, out):
+        if not t.is_cuda or t.stride(2) != 1:
+            raise KernelError("gemm_batched: operands must be CUDA tensors with contiguous last dimensions")
+    _check(load().xs_gemm_batched(x.data_ptr(), x.stride(1), x.stride(0), w.data_ptr(), w.stride(1), w.stride(0),
+                                  out.data_ptr(), out.stride(1), out.stride(0), B, M, N, K, _code(x), _stream()))
+
+
+# -------------------------------------------------------------------------------------- mamba-2
+def mamba2_conv(proj: torch.Tensor, col0: int, taps_w: torch.Tensor, bias: Optional[torch.Tensor], state: torch.Tensor,
+                seq_of_token: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(causal depthwise conv of proj[:, col0:col0 + C] + bias), inputs before the step from `state`
+    [*, taps - 1, C], which is then moved on. taps_w: [C, taps], the last column the current token's."""
+    _need(out, "out", proj.dtype); _need(state, "state", proj.dtype); _need(taps_w, "taps", torch.float32)
+    T, C = out.shape
+    taps = taps_w.shape[1]
+    if proj.stride(1) != 1 or proj.shape[0] != T or proj.shape[1] < col0 + C or taps_w.shape[0] != C:
+        raise KernelError(f"mamba2_conv: proj {tuple(proj.shape)}, taps {tuple(taps_w.shape)}, out {tuple(out.shape)}")
+    if taps > 1 and tuple(state.shape[1:]) != (taps - 1, C):
+        raise KernelError(f"mamba2_conv: state is {tuple(state.shape)}, expected [*, {taps - 1}, {C}]")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+    _check(load().xs_mamba2_conv(proj.data_ptr(), proj.stride(0), int(col0), taps_w.data_ptr(), _ptr(bias), state.data_ptr(),
+                                 seq_of_token.data_ptr(), cu_seqlens.data_ptr(), slots.data_ptr(), out.data_ptr(), T,
+                                 slots.numel(), C, taps, _code(proj), _stream()), kernels=2 if taps > 1 else 1)
+
+
+def mamba2_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col: int, dt_bias: torch.Tensor, a_log: torch.Tensor,
+                d_skip: torch.Tensor, state: torch.Tensor, cu_seqlens: torch.Tensor, slots: torch.Tensor, y: torch.Tensor,
+                heads: int, vdim: int, n_state: int, groups: int, chunks=None) -> None:
+    """The recurrence over a step's tokens; y [T, heads * vdim] float32 takes y_t * silu(z_t). state: [*, heads,
+    n_state, vdim] float32. `chunks` = (chunk_seq [n, 3] int32, first_chunk [n_seqs + 1] int32, chunk_state, chunk_decay)
+    runs long pieces chunk by chunk side by side."""
+    _need(xbc, "xbc", proj.dtype); _need(state, "state", torch.float32); _need(y, "y", torch.float32)
+    for t, name in ((dt_bias, "dt_bias"), (a_log, "A_log"), (d_skip, "D")):
+        _need(t, name, torch.float32)
+        if t.numel() != heads:
+            raise KernelError(f"mamba2_scan: {name} has {t.numel()} entries for {heads} heads")
+    if tuple(state.shape[1:]) != (heads, n_state, vdim):
+        raise KernelError(f"mamba2_scan: state is {tuple(state.shape)}, expected [*, {heads}, {n_state}, {vdim}]")
+    if xbc.shape[1] != heads * vdim + 2 * groups * n_state or proj.stride(1) != 1 or proj.shape[1] < dt_col + heads:
+        raise KernelError(f"mamba2_scan: xbc {tuple(xbc.shape)}, proj {tuple(proj.shape)}")
+    n_seqs = slots.numel()
+    if chunks is None:
+        _check(load().xs_mamba2_scan(xbc.data_ptr(), proj.data_ptr(), proj.stride(0), int(dt_col), dt_bias.data_ptr(),
+                                     a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu_seqlens.data_ptr(),
+                                     slots.data_ptr(), y.data_ptr(), n_seqs, heads, vdim, n_state, groups, _code(proj),
+                                     _stream()))
+        return
+    chunk_seq, first_chunk, chunk_state, chunk_decay = chunks
+    _need(chunk_seq, "chunk_seq", torch.int32); _need(first_chunk, "first_chunk", torch.int32)
+    _need(chunk_state, "chunk_state", torch.float32); _need(chunk_decay, "chunk_decay", torch.float32)
+    n = chunk_seq.shape[0]
+    if chunk_state.numel() < n * heads * n_state * vdim or chunk_decay.numel() < n * heads:
+        raise KernelError("mamba2_scan: the chunks' scratch is too small")
+    _check(load().xs_mamba2_scan_chunked(xbc.data_ptr(), proj.data_ptr(), proj.stride(0), int(dt_col), dt_bias.data_ptr(),
+                                         a_log.data_ptr(), d_skip.data_ptr(), state.data_ptr(), cu_seqlens.data_ptr(),
+                                         slots.data_ptr(), y.data_ptr(), chunk_state.data_ptr(), chunk_decay.data_ptr(),
+                                         chunk_seq.data_ptr(), first_chunk.data_ptr(), n, n_seqs, heads, vdim, n_state,
+                                         groups, _code(proj), _stream()), kernels=3)

@@ -1,11 +1,16 @@
 """The parts a layer is put together from. Importing this package registers them."""
 from .base import FeedForward, KVNeed, Mixer, Norm, Part, StateNeed, TensorSpec
 from .norm import RMSNorm
-from .rope import RotaryTable
+from .layernorm import LayerNorm
+from .rope import RotaryTable, ScaledRotaryTable
 from .attention import AttentionMixer
 from .short_conv import ShortConvMixer
 from .swiglu import SwiGLU
+from .latent_attention import LatentAttentionMixer
+from .mamba2 import Mamba2Mixer
+from .gated_units import ClampedGLU, RoutedExperts
 from .block import Block, ResidualStream
 
 __all__ = ["FeedForward", "KVNeed", "Mixer", "Norm", "RMSNorm", "Part", "StateNeed", "TensorSpec", "RotaryTable",
-           "AttentionMixer", "ShortConvMixer", "SwiGLU", "Block", "ResidualStream"]
+           "AttentionMixer", "ShortConvMixer", "SwiGLU", "Block", "ResidualStream", "LayerNorm", "ScaledRotaryTable",
+           "LatentAttentionMixer", "Mamba2Mixer", "ClampedGLU", "RoutedExperts"]

@@ -45,16 +45,18 @@ from typing import Dict, Optional, Tuple
 @dataclass(frozen=True)
 class TensorSpec:
     shape: Tuple[int, ...]
-    init: str = "normal"     # random-weights mode: "normal" N(0, std) | "ones" | "zeros"
+    init: str = "normal"     # random-weights mode: "normal" N(0, std) | "ones" | "zeros" | "uniform:lo:hi"
     role: str = "matrix"     # "matrix": held in the compute dtype; "vector": held in float32
 
 
 @dataclass(frozen=True)
 class KVNeed:
-    """Keys and values for every cached position (window 0) or the last `window` of them."""
+    """Keys and values for every cached position (window 0) or the last `window` of them. `planes` 1: one vector
+    a position and head instead of a key and a value (a latent from which both are made)."""
     kv_heads: int
     head_dim: int
     window: int = 0
+    planes: int = 2
 
 
 @dataclass(frozen=True)

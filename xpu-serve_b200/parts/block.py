@@ -140,11 +140,15 @@ class Block:
         feed-forward's."""
         out: Dict[str, TensorSpec] = {}
         norm_cls = registry.norm_class(layer.norm.kind)
-        keys = ["pre_mixer", "pre_ffn"] + (["post_mixer", "post_ffn"] if layer.sandwich else [])
+        # (a layer without a feed-forward has no norms for one either; the order is the one random weights are drawn in)
+        keys = ["pre_mixer"] + (["pre_ffn"] if layer.ffn is not None else [])
+        if layer.sandwich:
+            keys += ["post_mixer"] + (["post_ffn"] if layer.ffn is not None else [])
         for key in keys:
             out.update(norm_cls.tensors(layer.norm, layer.names[key]))
         out.update(registry.mixer_class(layer.mixer.kind).tensors(layer.mixer))
-        out.update(registry.ffn_class(layer.ffn.kind).tensors(layer.ffn))
+        if layer.ffn is not None:
+            out.update(registry.ffn_class(layer.ffn.kind).tensors(layer.ffn))
         return out
 
     @classmethod
@@ -155,13 +159,13 @@ class Block:
         """`weights`: this layer's tensors by their names under the layer's prefix."""
         self.spec, self.rt = spec, rt
         self.mixer = registry.mixer_class(spec.mixer.kind)(spec.mixer, weights, rt)
-        self.ffn = registry.ffn_class(spec.ffn.kind)(spec.ffn, weights, rt)
+        self.ffn = registry.ffn_class(spec.ffn.kind)(spec.ffn, weights, rt) if spec.ffn is not None else None
         n = spec.names
         norm_cls = registry.norm_class(spec.norm.kind)
         self.pre_mixer = norm_cls(spec.norm, weights, n["pre_mixer"], rt)
-        self.pre_ffn = norm_cls(spec.norm, weights, n["pre_ffn"], rt)
+        self.pre_ffn = norm_cls(spec.norm, weights, n["pre_ffn"], rt) if self.ffn is not None else None
         self.post_mixer = norm_cls(spec.norm, weights, n["post_mixer"], rt) if spec.sandwich else None
-        self.post_ffn = norm_cls(spec.norm, weights, n["post_ffn"], rt) if spec.sandwich else None
+        self.post_ffn = norm_cls(spec.norm, weights, n["post_ffn"], rt) if spec.sandwich and self.ffn is not None else None
         self.first_norm = self.pre_mixer      # the norm that reads the stream first: what the block before may prepare
 
     def forward(self, stream: ResidualStream, step, cache, next_norm: Optional[Norm] = None) -> None:
@@ -171,13 +175,16 @@ class Block:
         rows = stream.h.shape[0]
         # (a part whose first product runs elsewhere at this number of rows gets the normed tensor, and the product
         # before it does not prepare the norm's input for it; its last product may still add to the stream itself)
-        ffn_lazy = fuse and self.ffn.fuses_norm and self.ffn.takes_prenormed(rows)
+        ffn_lazy = fuse and self.ffn is not None and self.ffn.fuses_norm and self.ffn.takes_prenormed(rows)
         if fuse and self.mixer.fuses_norm:
             x = stream.norm_input(self.pre_mixer, lazy=self.mixer.takes_prenormed(rows))
-            self.mixer.forward(x, step, cache, into=stream.sink(self.pre_ffn if ffn_lazy else None))
+            after = (self.pre_ffn if ffn_lazy else None) if self.ffn is not None else next_norm
+            self.mixer.forward(x, step, cache, into=stream.sink(after))
         else:
             x = stream.norm(self.pre_mixer)
             stream.add(self.mixer.forward(x, step, cache), self.post_mixer)
+        if self.ffn is None:
+            return
         if fuse and self.ffn.fuses_norm:
             y = stream.norm_input(self.pre_ffn, lazy=ffn_lazy)
             self.ffn.forward(y, step, into=stream.sink(next_norm))

@@ -1,0 +1,95 @@
+"""Two more feed-forwards: a clamped gated unit, and routed experts.
+
+ClampedGLU:     down(g * sigmoid(alpha g) * (u + up_shift)), g = min(gate x, limit), u = clamp(up x, -limit, limit).
+RoutedExperts:  `experts` SwiGLU feed-forwards without biases; a token's router logits (float32) choose the `top`
+                largest, whose softmax over themselves weights the chosen experts' outputs. On the device the step's
+                (token, choice) rows are sorted by expert and the two products walk row tiles of one expert each
+                (csrc/experts.cu); no count ever reaches the host, so a step with experts can be captured in a graph.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .. import registry
+from ..ops import lib as ops
+from .base import FeedForward, TensorSpec
+
+
+class ClampedGLU(FeedForward):
+    kind = "clamped_glu"
+    fixed_shape_ok = True
+
+    @classmethod
+    def tensors(cls, spec) -> Dict[str, TensorSpec]:
+        n = spec.names
+        return {n["gate"]: TensorSpec((spec.intermediate, spec.hidden)),
+                n["up"]: TensorSpec((spec.intermediate, spec.hidden)),
+                n["down"]: TensorSpec((spec.hidden, spec.intermediate))}
+
+    def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
+        self.spec, self.rt = spec, rt
+        n = spec.names
+        self.w_gate_up = rt.matrix(torch.cat([weights[n["gate"]].to(torch.float32), weights[n["up"]].to(torch.float32)], 0))
+        self.w_down = rt.matrix(weights[n["down"]])
+
+    def forward(self, y, step) -> torch.Tensor:
+        rt, s = self.rt, self.spec
+        gu = rt.linear(y, self.w_gate_up, "ffn_gate_up")
+        act = rt.ws.get("ffn_act", (y.shape[0], s.intermediate), rt.act_dtype)
+        ops.clamped_glu(gu, act, s.limit, s.alpha, s.up_shift)
+        return rt.linear(act, self.w_down, "ffn_out")
+
+
+class RoutedExperts(FeedForward):
+    kind = "routed_experts"
+    fixed_shape_ok = True
+
+    @classmethod
+    def tensors(cls, spec) -> Dict[str, TensorSpec]:
+        n = spec.names
+        out = {}
+        for e in range(spec.experts):
+            out[n["gate"].format(e=e)] = TensorSpec((spec.intermediate, spec.hidden))
+            out[n["up"].format(e=e)] = TensorSpec((spec.intermediate, spec.hidden))
+            out[n["down"].format(e=e)] = TensorSpec((spec.hidden, spec.intermediate))
+        out[n["router"]] = TensorSpec((spec.experts, spec.hidden))
+        return out
+
+    def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
+        if spec.top > 16:
+            raise ValueError(f"routed experts: top {spec.top} (at most 16 are supported)")
+        self.spec, self.rt = spec, rt
+        n = spec.names
+        # [experts, 2 F, hidden] with an expert's gate rows before its up rows, and [experts, hidden, F]
+        self.w_gate_up = rt.matrix(torch.stack([
+            torch.cat([weights[n["gate"].format(e=e)].to(torch.float32), weights[n["up"].format(e=e)].to(torch.float32)], 0)
+            for e in range(spec.experts)]))
+        self.w_down = rt.matrix(torch.stack([weights[n["down"].format(e=e)].to(torch.float32) for e in range(spec.experts)]))
+        self.w_router = rt.matrix(weights[n["router"]])
+
+    def forward(self, y, step) -> torch.Tensor:
+        rt, s = self.rt, self.spec
+        T, n = y.shape[0], y.shape[0] * s.top
+        ws = rt.ws
+        logits = ws.get("moe_logits", (T, s.experts), torch.float32)
+        ops.gemm_generic(y, self.w_router, logits)          # float32 sums of the activation type's products, not rounded
+        ids = ws.get("moe_ids", (n,), torch.int32)
+        wts = ws.get("moe_wts", (n,), torch.float32)
+        place = ws.get("moe_place", (n,), torch.int32)
+        source = ws.get("moe_source", (n,), torch.int32)
+        meta = ws.get("moe_meta", (4 + 3 * ops.moe_max_tiles(n, s.experts),), torch.int32)
+        ops.moe_route(logits, s.top, ids, wts)
+        ops.moe_plan(ids, s.experts, place, source, meta)
+        act = ws.get("moe_act", (n, s.intermediate), rt.act_dtype)
+        ops.moe_gemm(y, self.w_gate_up, act, meta, n, source, s.top, glu=True)
+        rows_out = ws.get("moe_rows", (n, s.hidden), rt.act_dtype)
+        ops.moe_gemm(act, self.w_down, rows_out, meta, n, None, s.top, glu=False)
+        out = ws.get("ffn_out", (T, s.hidden), rt.act_dtype)
+        ops.moe_combine(rows_out, place, wts, out, s.top)
+        return out
+
+
+registry.register_ffn(ClampedGLU.kind, ClampedGLU)
+registry.register_ffn(RoutedExperts.kind, RoutedExperts)

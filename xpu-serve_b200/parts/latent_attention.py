@@ -1,0 +1,101 @@
+"""Latent attention: the keys and values of all heads are made from one cached vector per position.
+
+    q = Wq x                       per head [dim unrotated | rot_dim rotated]
+    d = Wdown x                    [kv_rank + rot_dim]
+    c = d[:kv_rank] / rms(d[:kv_rank]) * w_norm          the latent; k_rot = rotate(d[kv_rank:]), one for all heads
+    key_h = [Wuk_h c | k_rot],  value_h = Wuv_h c,  score = scale * (q_h . key_h)
+
+The cache keeps [c | k_rot] per position and nothing per head. Both per-head matrices are applied on the query's and the
+output's side (q~_h = Wuk_h^T q_h[:dim]; out_h = Wuv_h sum_j p_j c_j), so the attention kernel reads cache rows only
+(csrc/latent_attention.cu) and a step's cost does not depend on how many positions are cached per head. Options: a
+window, a sink per head in the softmax's denominator, a sigmoid gate per head from the mixer's own input. One matrix
+product gives q, d and the gate logits (their weights are stacked at load).
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .. import registry
+from ..ops import lib as ops
+from .base import KVNeed, Mixer, TensorSpec
+
+
+class LatentAttentionMixer(Mixer):
+    kind = "latent_attention"
+    fixed_shape_ok = True
+
+    @classmethod
+    def tensors(cls, spec) -> Dict[str, TensorSpec]:
+        n, H = spec.names, spec.heads
+        out = {
+            n["q"]: TensorSpec((H * (spec.dim + spec.rot_dim), spec.hidden)),
+            n["down"]: TensorSpec((spec.kv_rank + spec.rot_dim, spec.hidden)),
+            n["latent_norm"]: TensorSpec((spec.kv_rank,), init="ones", role="vector"),
+            n["up_k"]: TensorSpec((H * spec.dim, spec.kv_rank)),
+            n["up_v"]: TensorSpec((H * spec.vdim, spec.kv_rank)),
+        }
+        if spec.head_gate:
+            out[n["gate"]] = TensorSpec((H, spec.hidden))
+        if spec.sink:
+            out[n["sink"]] = TensorSpec((H,), role="vector")
+        out[n["o"]] = TensorSpec((spec.hidden, H * spec.vdim))
+        return out
+
+    @classmethod
+    def cache_need(cls, spec):
+        return KVNeed(1, spec.kv_rank + spec.rot_dim, spec.window, planes=1)
+
+    def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
+        self.spec, self.rt = spec, rt
+        n, H = spec.names, spec.heads
+        if spec.position is not None and spec.position.head_dim != spec.rot_dim:
+            raise ValueError("latent attention: the rotation's vector is the rotated part of a head")
+        rows = [weights[n["q"]], weights[n["down"]]]
+        if spec.head_gate:
+            g = weights[n["gate"]]
+            pad = (-g.shape[0]) % 16
+            rows.append(torch.cat([g, torch.zeros(pad, g.shape[1], dtype=g.dtype)], 0) if pad else g)
+        self.w_in = rt.matrix(torch.cat([r.to(torch.float32) for r in rows], 0))
+        self.q_cols = H * (spec.dim + spec.rot_dim)
+        self.down_cols = spec.kv_rank + spec.rot_dim
+        self.w_norm = rt.vector(weights[n["latent_norm"]])
+        # Wuk_h^T as [heads, kv_rank, dim] and Wuv_h as [heads, vdim, kv_rank]: the two batched products' weights
+        self.w_uk_t = rt.matrix(weights[n["up_k"]].to(torch.float32).view(H, spec.dim, spec.kv_rank).transpose(1, 2))
+        self.w_uv = rt.matrix(weights[n["up_v"]].to(torch.float32).view(H, spec.vdim, spec.kv_rank))
+        self.sink = rt.vector(weights[n["sink"]]) if spec.sink else None
+        self.w_o = rt.matrix(weights[n["o"]])
+        self.position = (registry.position_class(spec.position.kind)(spec.position, rt)
+                         if spec.position is not None else None)
+
+    def forward(self, x, step, cache) -> torch.Tensor:
+        s, rt = self.spec, self.rt
+        T, H, R = x.shape[0], s.heads, s.kv_rank
+        if cache is None or cache.storage is None or not cache.owner:
+            raise RuntimeError("latent attention needs a cache of its own")
+        table = step.page_tables[cache.group]
+        proj = rt.linear(x, self.w_in, "lat_proj")
+        q = proj[:, :self.q_cols]
+        down = proj[:, self.q_cols:self.q_cols + self.down_cols]
+        gate = proj[:, self.q_cols + self.down_cols:] if s.head_gate else None
+        rope = self.position.table(step.max_positions) if self.position is not None else None
+        q_rot = rt.ws.get("lat_q_rot", (T, H, s.rot_dim), rt.act_dtype)
+        ops.latent_prepare(down, q, self.w_norm, rope, step.positions, step.seq_of_token, table, cache.storage, q_rot,
+                           H, s.dim, s.rot_dim, R, s.position.dims if s.position is not None else 0, step.page_size, s.eps)
+        q_lat = rt.ws.get("lat_q_lat", (H, T, R), rt.act_dtype)
+        rt.batched_product(q.unflatten(1, (H, s.dim + s.rot_dim))[:, :, :s.dim].transpose(0, 1), self.w_uk_t, q_lat)
+        o_lat = rt.ws.get("lat_o_lat", (H, T, R), rt.act_dtype)
+        self.attend(q_lat, q_rot, cache, table, step, gate, o_lat)
+        o = rt.ws.get("lat_o", (T, H, s.vdim), rt.act_dtype)
+        rt.batched_product(o_lat, self.w_uv, o.transpose(0, 1))
+        return rt.linear(o.view(T, H * s.vdim), self.w_o, "mixer_out")
+
+    def attend(self, q_lat, q_rot, cache, table, step, gate, o_lat) -> None:
+        """q_lat, o_lat: [heads, tokens, kv_rank]."""
+        s = self.spec
+        ops.latent_attention_generic(q_lat.transpose(0, 1), q_rot, cache.storage, table, step.seq_of_token, step.positions,
+                                     gate, self.sink, o_lat.transpose(0, 1), step.page_size, s.scale, s.window)
+
+
+registry.register_mixer(LatentAttentionMixer.kind, LatentAttentionMixer)

@@ -44,11 +44,13 @@ def architecture_for(config_json: dict) -> Architecture:
     archs = config_json.get("architectures")
     if isinstance(archs, list):
         names += [a for a in archs if isinstance(a, str)]
+    if isinstance(config_json.get("architecture"), str):      # a config.json that names its design under this key
+        names.append(config_json["architecture"])
     for n in names:
         if n in _ARCHITECTURES:
             return _ARCHITECTURES[n]
     raise ConfigError(
-        f"config.json: model_type {model_type!r} is not supported "
+        f"config.json: model_type {(model_type or config_json.get('architecture'))!r} is not supported "
         f"(supported: {', '.join(supported_architectures())})")
 
 

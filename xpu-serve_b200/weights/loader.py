@@ -10,6 +10,7 @@ built (src/models/lfm3/lfm3_decoder.cpp:100-103).
 """
 from __future__ import annotations
 
+import re
 import warnings
 from typing import Dict, List
 
@@ -38,8 +39,10 @@ def check_store(spec: ModelSpec, store: WeightStore) -> str:
     # that prefix, and the head's, are this model's to judge: the rest is read by name and left alone, as the
     # reference does (src/io/safetensors.cpp:14-18). Under the plain prefix every stray tensor is named.
     wrapped = prefix != spec.prefixes[-1]
+    ignorable = [re.compile(pat) for pat in spec.ignorable]
     unexpected = [n for n in store.names() if n not in expected
-                  and (not wrapped or n.startswith(prefix) or n == spec.names["head"])]
+                  and (not wrapped or n.startswith(prefix) or n == spec.names["head"])
+                  and not any(pat.search(n) for pat in ignorable)]
     wrong = [f"{n} is {list(store.shape(n))}, expected {list(ts.shape)}"
              for n, ts in expected.items() if n in store and tuple(store.shape(n)) != tuple(ts.shape)]
     bad_dtype = [f"{n} is {store.dtype(n)}" for n in expected

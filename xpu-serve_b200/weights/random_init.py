@@ -44,6 +44,9 @@ def random_tensors(spec, seed: int, dtype: str = "bfloat16", std: Optional[float
                 a = rng.uniform(norm_range[0], norm_range[1], size=ts.shape).astype(np.float32)
         elif ts.init == "zeros":
             a = np.zeros(ts.shape, dtype=np.float32)
+        elif ts.init.startswith("uniform:"):       # "uniform:lo:hi" (decay rates, step biases and the like)
+            lo, hi = (float(v) for v in ts.init.split(":")[1:3])
+            a = rng.uniform(lo, hi, size=ts.shape).astype(np.float32)
         else:
             a = rng.standard_normal(size=ts.shape, dtype=np.float32) * np.float32(sigma)
         if scale:
