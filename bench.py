@@ -52,6 +52,75 @@ WORKLOADS = {
     "ragged_2.6b": (family_shape(30, 2048, 32, 10752, 8192, range(2, 30, 3)), 16, (256, 4096), 512),
     "long_350m": (family_shape(16, 1024, 16, 6656, 32768, (2, 5, 8, 10, 12, 14)), 64, (1024, 24576), 256),
 }
+
+
+# Saralix layer stacks at sizes that resemble a real model's, each beside the closest LFM3 stack of equal width, layer count,
+# vocabulary and active feed-forward width (`--workload saralix`; random weights).
+def _latent(heads, dim, rot, vdim, rank, window=None):
+    m = {"heads": heads, "dim": dim, "rot_dim": rot, "vdim": vdim, "kv_rank": rank, "scale": (dim + rot) ** -0.5,
+         "rot": {"base": 10000.0, "dims": rot, "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+    if window:
+        m["mask"] = {"size": window}
+    return m
+
+
+_MOE = {"kind": "moe", "expert": {"ff": 1024}, "router": {"experts": 16, "top": 4}}
+_DENSE = {"kind": "dense", "ff": 8192, "limit": 7.0}
+_MAMBA = {"heads": 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}
+SARALIX_STACKS = {
+    # name: (Saralix layers, the LFM3 stack beside it: layer types, feed-forward width, window)
+    "latent_dense": ([("latent_attention", _latent(16, 128, 64, 128, 512), _DENSE)] * 2, (["full_attention"] * 2, 8192, 0)),
+    "window_experts": ([("latent_attention_2", _latent(16, 128, 64, 128, 512, window=1024), _MOE)] * 2,
+                       (["sliding_attention"] * 2, 4096, 1024)),
+    "mamba2_experts": ([("mamba2", _MAMBA, _MOE)] * 2, (["conv"] * 2, 4096, 0)),
+}
+
+
+def saralix_stack_configs(name: str, width: int = 2048, vocab: int = 32768):
+    layers, (kinds, ffn, window) = SARALIX_STACKS[name]
+    ours = {"architecture": "Saralix", "width": width, "vocab": vocab, "norm": {"eps": 1e-5},
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in layers]}
+    beside = dict(SHAPE_1_2B)
+    beside.update(vocab_size=vocab, hidden_size=width, intermediate_size=ffn, num_hidden_layers=len(kinds), layer_types=kinds,
+                  max_position_embeddings=CONTEXT)
+    beside.pop("rope_theta")
+    beside["rope_parameters"] = {k: {"rope_theta": 1000000.0} for k in set(kinds) if k != "conv"}
+    if window:
+        beside["sliding_window"] = window
+    return ours, beside
+
+
+def run_saralix_stacks(batch: int, steps: int, warmup: int, only=None) -> int:
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 after 2,048-token prompts, CUDA graph) of
+    each Saralix stack and of the LFM3 stack beside it, device-timed as the headline's points are."""
+    import torch
+    from xpu_serve_b200 import load_model
+    from xpu_serve_b200.config import Lfm3Config, SaralixConfig
+    from xpu_serve_b200.weights import write_random_model
+    points = {}
+    for name in SARALIX_STACKS:
+        if only and name not in only:
+            continue
+        ours, beside = saralix_stack_configs(name)
+        points[name] = {}
+        for label, config in (("saralix", SaralixConfig.from_json(ours)), ("lfm3", Lfm3Config.from_json(beside))):
+            with tempfile.TemporaryDirectory() as root:
+                folder = write_random_model(os.path.join(root, label), config, seed=0, dtype="bfloat16", std=0.02)
+                model = load_model(folder, dtype="bfloat16")
+            V = config.model_spec().vocab
+            prefill_ms = time_prefill(model, V, warmup=max(3, warmup // 2), runs=7)
+            ms, launches = time_decode(model, batch, steps, warmup, V)
+            points[name][label] = {"prefill_ms": round(prefill_ms, 3), "prefill_tok_s": round(PROMPT * 1000.0 / prefill_ms, 1),
+                                   "decode_ms_per_step": round(ms, 4), "decode_tok_s": round(batch * 1000.0 / ms, 1),
+                                   "launches_per_step": round(launches, 1)}
+            del model
+            torch.cuda.empty_cache()
+    print(json.dumps({"workload": "saralix", "metric": "prefill tok/s (2,048 tokens) and decode tok/s (batch %d) of two-layer stacks" % batch,
+                      "dtype": "bf16", "data": "synthetic token ids, random weights N(0, 0.02)", "steps": steps, "warmup": warmup,
+                      "width": 2048, "vocab": 32768, "points": points}))
+    return 0
+
+
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -367,7 +436,8 @@ def main() -> int:
                          "at long context), which the default run adds to `points`")
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "sample"],
                     help="time one part only and print a short line (for profiler captures)")
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS),
+    ap.add_argument("--stacks", default=None, help="with --workload saralix: a comma list of the stacks to run (all)")
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + ["saralix"],
                     help="instead of the default run: a batch of unequal prompts at another shape of the family")
     args = ap.parse_args()
 
@@ -381,6 +451,8 @@ def main() -> int:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.workload == "saralix":
+        return run_saralix_stacks(args.batch or 8, args.steps or 128, args.warmup, args.stacks.split(",") if args.stacks else None)
     if args.workload is not None:
         return run_workload(args.workload, args.layers, args.batch, args.steps)
     args.batch = args.batch or 8

@@ -48,7 +48,7 @@ def replayers(folders):
 
 
 _REFS = {}
-CLOSE_CALL = {"float32": 1e-5, "bfloat16": 0.04}
+CLOSE_CALL = {"float32": 1e-5, "bfloat16": 0.015}
 
 
 def reference(folder, name, requests, dtype="float32"):
@@ -74,7 +74,7 @@ def check(name, dtype, steps, requests, replayers, folders, max_tokens=1024):
     got = tu.collect(steps, tu.run_in_process(rp, steps), tiny.CONFIGS[name]["vocab"])
     ref = reference(folders(name, dtype), name, requests, dtype)
     ref = {k: v for k, v in ref.items() if k in got}
-    assert len(ref) >= len(got) // 3, "too many of the test's own tokens are close calls of a router; pick other prompts"
+    assert len(ref) >= min(len(got), 8), "the test's first tokens are close calls of a router; pick other prompts"
     gap, where, cos = tu.worst_gap({k: v for k, v in got.items() if k in ref}, ref)
     tol = tiny.upper_limit(name, dtype)
     print(f"GAP saralix {name} {dtype} steps={len(steps)} gap={gap:.3e} at {where} cos={cos:.7f} tol={tol:.1e}")
@@ -97,14 +97,14 @@ def test_one_mechanism_alone(name, dtype, replayers, folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["M", "N"])
+@pytest.mark.parametrize("name", ["M", "N", "D"])
 def test_whole(name, dtype, replayers, folders):
     reqs = requests_for(name)
     check(name, dtype, tu.whole_trace(reqs), reqs, replayers, folders)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["M", "N"])
+@pytest.mark.parametrize("name", ["M", "N", "D"])
 def test_prefill_then_token_by_token(name, dtype, replayers, folders):
     reqs = requests_for(name)
     check(name, dtype, tu.tail_trace(reqs, tail=32), reqs, replayers, folders)
@@ -112,17 +112,17 @@ def test_prefill_then_token_by_token(name, dtype, replayers, folders):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("batch", [3, 5, 13])
-@pytest.mark.parametrize("name", ["M", "N"])
+@pytest.mark.parametrize("name", ["M", "N", "D"])
 def test_unequal_batches_one_after_another(name, batch, dtype, replayers, folders):
     """Batches of unequal requests against each alone (the reference runs each alone); a later batch takes the slots
     and pages that the one before gave back, in a cache that holds little more than one batch."""
     reqs = requests_for(name)
-    check(name, dtype, tu.batch_trace(reqs, batch), reqs, replayers, folders, max_tokens=640)
+    check(name, dtype, tu.batch_trace(reqs, batch), reqs, replayers, folders, max_tokens=1280)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("pieces", [(2, 3, 64, 5), (7, 64, 65, 129, 3, 16, 40), (130, 2)])
-@pytest.mark.parametrize("name", ["M", "N"])
+@pytest.mark.parametrize("name", ["M", "N", "D"])
 def test_prompts_in_pieces(name, pieces, dtype, replayers, folders):
     """Pieces of several sizes, down to two tokens, at page borders and across windows, in steps that mix a later piece
     of one request with single tokens of others."""
@@ -131,7 +131,7 @@ def test_prompts_in_pieces(name, pieces, dtype, replayers, folders):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["M", "N"])
+@pytest.mark.parametrize("name", ["M", "N", "D"])
 def test_long_decoding(name, dtype, replayers, folders):
     """A short prompt and 200 tokens one by one: past both windows, over three page borders, with the recurrent state
     carried through every step; beside it a second request that ends early."""
@@ -143,7 +143,7 @@ def test_a_lost_part_is_caught(replayers, folders, monkeypatch):
     """The bounds see a sink that is left out, a window one token too long, and a state that is not carried."""
     from xpu_serve_b200.ops import lib as ops
     from xpu_serve_b200.parts.latent_attention import LatentAttentionMixer
-    reqs = requests_for("M", [40, 70])
+    reqs = requests_for("D", [40, 70])
     steps = tu.tail_trace(reqs, tail=10)
     real = ops.latent_attention_generic
 
@@ -157,14 +157,15 @@ def test_a_lost_part_is_caught(replayers, folders, monkeypatch):
         monkeypatch.setattr(ops, "latent_attention_generic", fault)
         monkeypatch.setattr(LatentAttentionMixer, "fast_path", lambda self, step: False, raising=False)
         with pytest.raises(AssertionError):
-            check("M", "bfloat16", steps, reqs, replayers, folders)
+            check("D", "bfloat16", steps, reqs, replayers, folders)
         monkeypatch.undo()
-    rp = replayers("M", "bfloat16")
-    monkeypatch.setattr(rp.cache.groups[[i for i, g in enumerate(rp.cache.groups) if not hasattr(g, "pages")][-1]], "zero",
-                        lambda slots: None)
-    check("M", "bfloat16", steps, reqs, replayers, folders)             # leaves states behind in the slots
+    rp = replayers("D", "bfloat16")
+    for g in rp.cache.groups:
+        if not hasattr(g, "pages"):                 # the groups of fixed-size state: opening a slot no longer zeroes it
+            monkeypatch.setattr(g, "zero", lambda slots: None)
+    check("D", "bfloat16", steps, reqs, replayers, folders)             # leaves states behind in the slots
     with pytest.raises(AssertionError):
-        check("M", "bfloat16", steps, reqs, replayers, folders)         # ... which the same slots now start from
+        check("D", "bfloat16", steps, reqs, replayers, folders)         # ... which the same slots now start from
 
 
 # ------------------------------------------------------------------------------ the attention kernel with planted keys
@@ -184,9 +185,10 @@ def plain_latent_attention(q_lat, q_rot, rows, pos, scale, window, sink, gate):
     return out
 
 
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("kernel,dtype", [("generic", torch.float32), ("generic", torch.bfloat16), ("mma", torch.bfloat16),
+                                          ("mma split", torch.bfloat16)])
 @pytest.mark.parametrize("window,sink,gate", [(0, False, True), (37, True, False), (64, True, True), (1, True, False)])
-def test_latent_attention_kernel_with_planted_keys(dtype, window, sink, gate):
+def test_latent_attention_kernel_with_planted_keys(kernel, dtype, window, sink, gate):
     """Queries of several sequences in one launch (a prompt piece and single tokens), pages in a shuffled order. One key
     far back, one at a page's last place, one just inside and one just outside the window are made to dominate (their
     row is the query's direction, scaled), so leaving one out or letting one in changes the result by far more than
@@ -229,8 +231,15 @@ def test_latent_attention_kernel_with_planted_keys(dtype, window, sink, gate):
     sink_t = (torch.randn(H) * 2).cuda() if sink else None
     out = torch.empty(T, H, R, dtype=dtype, device="cuda")
     dev = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
-    ops.latent_attention_generic(q_lat_d, q_rot_d, pool, table.cuda(), dev(seq_of), dev(positions), gate_t, sink_t, out,
-                                 page, 0.9, window)
+    if kernel == "generic":
+        ops.latent_attention_generic(q_lat_d, q_rot_d, pool, table.cuda(), dev(seq_of), dev(positions), gate_t, sink_t, out,
+                                     page, 0.9, window)
+    else:       # the tensor-core kernel, whole and with every sequence's pages cut over three CTAs
+        splits = 3 if "split" in kernel else 1
+        scratch = torch.empty(ops.latent_attention_mma_scratch_bytes(T * H, R, splits) + 16, dtype=torch.uint8, device="cuda")
+        cu = dev([0] + list(np.cumsum(q_lens)))
+        ops.latent_attention_mma(q_lat_d, q_rot_d, pool, table.cuda(), cu, dev(lens), gate_t, sink_t, out, scratch, len(lens),
+                                 max(q_lens), page, 0.9, window, splits)
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     for t in range(T):
         ref = plain_latent_attention(q_lat_d[t].double().cpu().numpy(), q_rot_d[t].double().cpu().numpy(), rows_of[seq_of[t]],
@@ -270,3 +279,53 @@ def test_greedy_generation_through_the_engine(folders, chunk):
         assert r.finish == "length" and r.tokens == want
     engine.stepper.cache.check()
     assert engine.stepper.cache.slots.held_count == 0
+
+
+@pytest.mark.parametrize("tokens,experts,top,width,ff", [(9, 5, 2, 64, 24), (300, 6, 3, 72, 40), (130, 3, 1, 256, 136)])
+def test_routed_products_on_tensor_cores(tokens, experts, top, width, ff):
+    """The plan with padded tiles, the gather, both grouped tcgen05 products and the combine, against float64: some
+    experts with no row, some with more than one tile, widths that are no multiple of the tiles."""
+    from xpu_serve_b200.ops import lib as ops
+    g = torch.Generator().manual_seed(tokens)
+    x = (torch.randn(tokens, width, generator=g) * 0.5).bfloat16()
+    w_gate = (torch.randn(experts, ff, width, generator=g) * 0.2).bfloat16()
+    w_up = (torch.randn(experts, ff, width, generator=g) * 0.2).bfloat16()
+    w_down = (torch.randn(experts, width, ff, generator=g) * 0.2).bfloat16()
+    logits = torch.randn(tokens, experts, generator=g)
+    logits[:, 1] -= 50.0                                    # an expert that nobody chooses
+    n = tokens * top
+    dev = "cuda"
+    ids = torch.empty(n, dtype=torch.int32, device=dev)
+    wts = torch.empty(n, dtype=torch.float32, device=dev)
+    place = torch.empty(n, dtype=torch.int32, device=dev)
+    tiles = ops.moe_max_tiles_of(n, experts, 128)
+    source = torch.empty(128 * tiles, dtype=torch.int32, device=dev)
+    meta = torch.empty(4 + 3 * tiles, dtype=torch.int32, device=dev)
+    ops.moe_route(logits.to(dev), top, ids, wts)
+    ops.moe_plan(ids, experts, place, source, meta, tile_rows=128)
+    rows_in = torch.empty(128 * tiles, width, dtype=torch.bfloat16, device=dev)
+    ops.moe_gather(x.to(dev), source, top, rows_in)
+    stacked = torch.stack([torch.stack([w_gate[e].view(ff // 8, 8, width), w_up[e].view(ff // 8, 8, width)], 1).reshape(2 * ff, width)
+                           for e in range(experts)]).to(dev)
+    act = torch.empty(128 * tiles, ff, dtype=torch.bfloat16, device=dev)
+    ops.gemm_tc_grouped(rows_in, stacked, act, meta, tiles, glu=True)
+    rows_out = torch.empty(128 * tiles, width, dtype=torch.bfloat16, device=dev)
+    ops.gemm_tc_grouped(act, w_down.to(dev), rows_out, meta, tiles, glu=False)
+    y = torch.empty(tokens, width, dtype=torch.bfloat16, device=dev)
+    ops.moe_combine(rows_out, place, wts, y, top)
+    torch.cuda.synchronize()
+    assert int(ops.gemm_tc_status(torch.device(dev)).item()) == 0
+    # float64, with the device's own choices checked against a plain top-k
+    order = torch.argsort(-logits, dim=1, stable=True)[:, :top]
+    assert torch.equal(ids.cpu().view(tokens, top).long(), order)
+    chosen = torch.gather(logits.double(), 1, order)
+    weight = torch.softmax(chosen, dim=1)
+    ref = torch.zeros(tokens, width, dtype=torch.float64)
+    xd = x.double()
+    for t in range(tokens):
+        for k in range(top):
+            e = int(order[t, k])
+            gt, up = w_gate[e].double() @ xd[t], w_up[e].double() @ xd[t]
+            ref[t] += weight[t, k] * (w_down[e].double() @ (gt / (1 + torch.exp(-gt)) * up))
+    gap = (y.double().cpu() - ref).abs().max() / ref.abs().max()
+    assert gap < 2e-2, gap

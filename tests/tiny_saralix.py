@@ -4,8 +4,8 @@ M mixes every mixer and feed-forward at sizes that are no multiple of 8 and diff
 sizes, ranks, groups, taps, experts): a gated latent attention with a stretched rotation, two Mamba-2 layers (one whose
 state has more rows than a thread keeps at a time is in N), a windowed latent attention with sinks, an unstretched
 rotation and no feed-forward at all, dense and routed feed-forwards (top 3 of 6). N has widths that are multiples of 8,
-a window longer than a cache page, one head, one expert chosen of three, and a state of 160 rows. The single-layer
-configurations run one mechanism alone.
+a window longer than a cache page, one head, one expert chosen of three, and a state of 160 rows. D has every mixer and
+no experts. The single-layer configurations run one mechanism alone.
 """
 import os
 
@@ -54,6 +54,13 @@ CONFIGS = {
         ("latent_attention_2", latent(1, 48, 16, 40, 96, 0.15, base=100000.0, scaling={"factor": 16.0, "original": 32, "fast": 16.0, "slow": 0.5},
                                       window=70), dense(256, 3.0)),
         ("latent_attention", latent(8, 16, 32, 8, 24, 0.18, base=777.0), moe(64, 8, 4)),
+    ]),
+    # every mixer, no experts: at reduced precision no router's close call stands between a fault and the bound
+    "D": model(64, 180, [
+        ("latent_attention_2", latent(4, 16, 16, 8, 48, 0.2, base=2000.0, scaling=STRETCH, window=21), dense(96, 2.5)),
+        ("mamba2", mamba(4, 16, 32, 4, 4, 2), None),
+        ("latent_attention", latent(2, 24, 8, 32, 16, 0.25, base=400.0), dense(40, 1.0)),
+        ("mamba2", mamba(8, 8, 8, 1, 3, 8), dense(72, 4.0)),
     ]),
     # one mechanism each (the feed-forward ones behind the smallest mixer)
     "gated": model(40, 150, [("latent_attention", latent(2, 14, 6, 10, 28, 0.25, base=900.0, scaling=STRETCH), None)]),

@@ -74,8 +74,9 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
 
 // ------------------------------------------------------------------------------------------------------------- plan
 // meta: [0] number of tiles; then per tile 3 words (expert, first row, rows) from meta[4] on.
-__global__ void moe_plan_kernel(const int32_t* __restrict__ ids, int n, int E, int tile_rows, int32_t* __restrict__ place,
-                                int32_t* __restrict__ source, int32_t* __restrict__ meta) {
+// pad: every expert's rows start at a multiple of tile_rows (places that no row takes get source -1; rows_cap places).
+__global__ void moe_plan_kernel(const int32_t* __restrict__ ids, int n, int E, int tile_rows, int pad, int rows_cap,
+                                int32_t* __restrict__ place, int32_t* __restrict__ source, int32_t* __restrict__ meta) {
     extern __shared__ int32_t sm[];      // count[E], first[E], next[E]
     int32_t* count = sm;
     int32_t* first = sm + E;
@@ -83,6 +84,8 @@ __global__ void moe_plan_kernel(const int32_t* __restrict__ ids, int n, int E, i
     pdl_launch_dependents();
     pdl_wait();
     for (int e = threadIdx.x; e < E; e += blockDim.x) count[e] = 0;
+    if (pad)
+        for (int i = threadIdx.x; i < rows_cap; i += blockDim.x) source[i] = -1;
     __syncthreads();
     for (int i = threadIdx.x; i < n; i += blockDim.x) atomicAdd(&count[ids[i]], 1);
     __syncthreads();
@@ -99,6 +102,7 @@ __global__ void moe_plan_kernel(const int32_t* __restrict__ ids, int n, int E, i
                 ++tiles;
             }
             at += count[e];
+            if (pad) at = (at + tile_rows - 1) / tile_rows * tile_rows;
         }
         meta[0] = tiles;
     }
@@ -203,6 +207,19 @@ moe_gemm_kernel(const TX* __restrict__ x, int64_t ldx, const TX* __restrict__ w,
     }
 }
 
+// ----------------------------------------------------------------------------------------------------------- gather
+// sorted[r, :] = x[source[r] / top, :] (zeros where source[r] < 0), 16 bytes a thread.
+__global__ void moe_gather_kernel(const uint4* __restrict__ x, int64_t ldx16, const int32_t* __restrict__ source, int top,
+                                  uint4* __restrict__ sorted, int K16) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.x;
+    const int src = source[r];
+    const uint4* from = x + (int64_t)(src < 0 ? 0 : src / top) * ldx16;
+    for (int c = threadIdx.x; c < K16; c += blockDim.x)
+        sorted[(int64_t)r * K16 + c] = src < 0 ? make_uint4(0u, 0u, 0u, 0u) : from[c];
+}
+
 // ---------------------------------------------------------------------------------------------------------- combine
 template <typename TI, typename TO>
 __global__ void moe_combine_kernel(const TI* __restrict__ rows_out, const int32_t* __restrict__ place,
@@ -247,11 +264,18 @@ XS_API int xs_moe_tile_rows() { return TM; }
 // How many tiles n rows over E experts can make at most: whole tiles, and a partly filled one per expert.
 XS_API int xs_moe_max_tiles(int n, int E) { return n / TM + (n < E ? n : E); }
 
-XS_API int xs_moe_plan(const int32_t* ids, int n, int E, int32_t* place, int32_t* source, int32_t* meta,
-                       cudaStream_t stream) {
+// tile_rows 0: the generic product's tiles, rows packed. tile_rows > 0: tiles of that many rows, every expert's rows
+// padded to whole tiles; `source` then has rows_cap >= tile_rows * xs_moe_max_tiles_of(n, E, tile_rows) places.
+XS_API int xs_moe_max_tiles_of(int n, int E, int tile_rows) { return n / tile_rows + (n < E ? n : E); }
+
+XS_API int xs_moe_plan(const int32_t* ids, int n, int E, int tile_rows, int rows_cap, int32_t* place, int32_t* source,
+                       int32_t* meta, cudaStream_t stream) {
     if (n == 0) return 0;
     XS_REQUIRE(n > 0 && E > 0 && E <= 4096, "moe_plan: %d rows, %d experts (at most 4096)", n, E);
-    xs_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int32_t), stream, ids, n, E, TM, place, source, meta);
+    XS_REQUIRE(tile_rows == 0 || rows_cap >= tile_rows * xs_moe_max_tiles_of(n, E, tile_rows), "moe_plan: %d places for %d rows in tiles of %d",
+               rows_cap, n, tile_rows);
+    xs_launch(moe_plan_kernel, dim3(1), dim3(1024), (size_t)3 * E * sizeof(int32_t), stream, ids, n, E,
+              tile_rows > 0 ? tile_rows : TM, tile_rows > 0 ? 1 : 0, rows_cap, place, source, meta);
     XS_LAUNCH_CHECK("moe_plan");
     return 0;
 }
@@ -276,6 +300,18 @@ XS_API int xs_moe_gemm(const void* x, int64_t ldx, const void* w, void* out, int
     XS_DISPATCH_DTYPE(in_dtype, TT, XS_GO(TT));
 #undef XS_GO
     XS_LAUNCH_CHECK("moe_gemm");
+    return 0;
+}
+
+// x rows of K bfloat16 (K a multiple of 8, rows 16-byte aligned) into the plan's padded order.
+XS_API int xs_moe_gather(const void* x, int64_t ldx, const int32_t* source, int top, void* sorted, int rows_cap, int K,
+                         cudaStream_t stream) {
+    if (rows_cap == 0) return 0;
+    XS_REQUIRE(K > 0 && K % 8 == 0 && ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)sorted % 16 == 0 && top > 0,
+               "moe_gather: rows of %d (stride %lld) are not 16-byte pieces", K, (long long)ldx);
+    xs_launch(moe_gather_kernel, dim3(rows_cap), dim3(K / 8 >= 256 ? 256 : 128), 0, stream, (const uint4*)x, ldx / 8, source, top,
+              (uint4*)sorted, K / 8);
+    XS_LAUNCH_CHECK("moe_gather");
     return 0;
 }
 

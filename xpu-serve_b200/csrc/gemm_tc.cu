@@ -651,6 +651,150 @@ int launch_persistent(const CUtensorMap& mx, const CUtensorMap& mw, const GemmTc
                      tiles_f) == cudaSuccess ? 0 : -1;
 }
 
+
+// ---- grouped products (routed experts) ------------------------------------------------------------------
+// The persistent kernel above over a list of row tiles that lives on the device: meta[0] tiles, tile i is the rows
+// [meta[5 + 3 i], + meta[6 + 3 i]) of x (a multiple of 128 apart: every expert's rows are padded to whole tiles) and
+// multiplies them with the weight of expert meta[4 + 3 i], rows [e * w_rows, (e + 1) * w_rows) of the stacked weight.
+// The grid is sized by the most tiles there can be; every role reads the true count after the wait and walks the same
+// tiles. A weight box that reaches past an expert's last row reads the next expert's (or zeros at the end): those
+// columns are not stored.
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_grouped_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_w,
+                       const GemmTcParams p, const int32_t* __restrict__ meta, int tiles_f, int w_rows) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* ring = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t bar_full[STAGES];
+    __shared__ __align__(8) uint64_t bar_empty[STAGES];
+    __shared__ __align__(8) uint64_t bar_acc_full[2];
+    __shared__ __align__(8) uint64_t bar_acc_empty[2];
+    __shared__ uint32_t tmem_base;
+    __shared__ int abort_flag;
+
+    constexpr uint32_t kTmemCols = 2 * BN;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_kb = (p.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(smem_u32(&bar_full[s]), 1);
+            mbar_init(smem_u32(&bar_empty[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&bar_acc_full[b]), 1);
+            mbar_init(smem_u32(&bar_acc_empty[b]), 4);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    pdl_launch_dependents();
+    pdl_wait();
+    volatile int* abort_p = &abort_flag;
+    const int m_tiles = meta[0];
+    const int total = m_tiles * tiles_f;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (int t = blockIdx.x; t < total && !*abort_p; t += gridDim.x) {
+                const int tile_f = t / m_tiles, mi = t % m_tiles;
+                const int e = meta[4 + 3 * mi], row0 = meta[5 + 3 * mi];
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (it >= STAGES && !mbar_wait(smem_u32(&bar_empty[s]), ((it / STAGES) & 1) ^ 1, abort_p)) break;
+                    const uint32_t full = smem_u32(&bar_full[s]);
+                    mbar_expect_tx(full, Smem<BN>::kStageBytes);
+                    tma_load_2d(smem_u32(ring + s * Smem<BN>::kStageBytes), &tmap_x, kb * BK, row0, full);
+                    tma_load_2d(smem_u32(ring + s * Smem<BN>::kStageBytes + Smem<BN>::kABytes), &tmap_w, kb * BK,
+                                e * w_rows + tile_f * BN, full);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BN);
+            int it = 0, lt = 0;
+            for (int t = blockIdx.x; t < total && !*abort_p; t += gridDim.x, ++lt) {
+                const int buf = lt & 1;
+                if (lt >= 2 && !mbar_wait(smem_u32(&bar_acc_empty[buf]), ((lt >> 1) & 1) ^ 1, abort_p)) break;
+                tcgen05_fence_after();
+                const uint32_t acc = tmem_base + (uint32_t)(buf * BN);
+                bool ok = true;
+                for (int kb = 0; kb < n_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(smem_u32(&bar_full[s]), (it / STAGES) & 1, abort_p)) { ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint32_t a_addr = smem_u32(ring + s * Smem<BN>::kStageBytes);
+                    const uint64_t da = smem_desc_sw128(a_addr), db = smem_desc_sw128(a_addr + Smem<BN>::kABytes);
+#pragma unroll
+                    for (int k = 0; k < BK / 16; ++k)
+                        umma_bf16(acc, da + (uint64_t)(k * 2), db + (uint64_t)(k * 2), idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tcgen05_commit(smem_u32(&bar_empty[s]));
+                }
+                if (!ok) break;
+                tcgen05_commit(smem_u32(&bar_acc_full[buf]));
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int lt = 0;
+        for (int t = blockIdx.x; t < total; t += gridDim.x, ++lt) {
+            const int tile_f = t / m_tiles, mi = t % m_tiles, buf = lt & 1;
+            const int row0 = meta[5 + 3 * mi], rows = meta[6 + 3 * mi];
+            if (!mbar_wait(smem_u32(&bar_acc_full[buf]), (lt >> 1) & 1, abort_p)) break;
+            tcgen05_fence_after();
+            const int local = quarter * 32 + lane;
+            const int token = row0 + local;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 32) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c), r);
+                if (local < rows) {
+                    emit16(p, r, token, tile_f * BN + c);
+                    emit16(p, r + 16, token, tile_f * BN + c + 16);
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_acc_empty[buf]));
+        }
+        tcgen05_fence_before();
+    }
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+    if (threadIdx.x == 0 && abort_flag) atomicExch(p.status, 1);
+}
+
+template <int BN, int STAGES>
+int launch_grouped(const CUtensorMap& mx, const CUtensorMap& mw, const GemmTcParams& p, const int32_t* meta, int max_m_tiles,
+                   int w_rows, cudaStream_t stream) {
+    const size_t smem = (size_t)STAGES * Smem<BN>::kStageBytes + 1024;
+    static bool opted = false;
+    static int sms = 0;
+    if (!opted) {
+        cudaFuncSetAttribute(gemm_tc_grouped_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        opted = true;
+    }
+    const int tiles_f = ceil_div_i(w_rows, BN);
+    const int64_t most = (int64_t)max_m_tiles * tiles_f;
+    const int grid = most < sms ? (int)most : sms;
+    return xs_launch(gemm_tc_grouped_kernel<BN, STAGES>, dim3(grid), dim3(kThreads), smem, stream, mx, mw, p, meta, tiles_f,
+                     w_rows) == cudaSuccess ? 0 : -1;
+}
+
 int g_pair = 1;   // CTA pairs for more than 128 tokens (xs_gemm_tc_set_pair)
 int g_few_deep = 0;   // few tokens: 1 = a deep ring and one CTA an SM; 0 = four stages and two CTAs an SM
 
@@ -783,5 +927,42 @@ XS_API int xs_gemm_tc(const void* x, const void* w, const float* bias, void* out
         else rc = launch_persistent<256, 4>(mx, mw, p, stream);
     }
     XS_REQUIRE(rc == 0, "gemm (tcgen05): launch failed: %s", cudaGetErrorString(cudaGetLastError()));
+    return 0;
+}
+
+
+// out[r] = W[expert of r's tile] . x[r] for the row tiles of a plan on the device (csrc/experts.cu: xs_moe_plan with
+// padding, tiles of 128 rows). x: [rows_cap, K] with every expert's rows padded to whole tiles; w: [E * N, K], the
+// experts' weights one under another; out: [rows_cap, N] (N / 2 with the SwiGLU epilogue, whose weight is stacked in
+// blocks of 8 gate and 8 up rows per expert). max_m_tiles: the most tiles the plan can hold (the grid's bound).
+XS_API int xs_gemm_tc_grouped(const void* x, const void* w, void* out, int out_dtype, int epilogue, const int32_t* meta,
+                              int max_m_tiles, int rows_cap, int E, int N, int K, int64_t ldx, int64_t ldo, int* status,
+                              cudaStream_t stream) {
+    if (max_m_tiles == 0 || N == 0) return 0;
+    XS_REQUIRE(xs_gemm_tc_supports(rows_cap, N, K, ldx, K), "gemm (tcgen05, grouped): rows %d, N %d, K %d, stride %lld not supported",
+               rows_cap, N, K, (long long)ldx);
+    XS_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm (tcgen05, grouped): operands must be 16-byte aligned");
+    XS_REQUIRE((epilogue == EPI_STORE || epilogue == EPI_SWIGLU) && status != nullptr && out != nullptr && meta != nullptr,
+               "gemm (tcgen05, grouped): bad arguments");
+    XS_REQUIRE(epilogue != EPI_SWIGLU || N % 16 == 0, "gemm (tcgen05, grouped): the fused activation needs N %% 16 == 0");
+    XS_REQUIRE(rows_cap >= max_m_tiles * BM && E > 0 && (int64_t)E * N < 2147483647, "gemm (tcgen05, grouped): %d rows for %d tiles",
+               rows_cap, max_m_tiles);
+    GemmTcParams p;
+    p.out = out;
+    p.bias = nullptr;
+    p.partials = nullptr;
+    p.counters = nullptr;
+    p.status = status;
+    p.T = rows_cap; p.N = N; p.K = K; p.ksplit = 1; p.epilogue = epilogue; p.out_f32 = out_dtype == XS_F32;
+    p.ldo = ldo;
+    const int esz = p.out_f32 ? 4 : 2;
+    p.vec = ((uintptr_t)out % 16 == 0) && ((ldo * esz) % 16 == 0);
+    alignas(64) CUtensorMap mw, mx;
+    const int box_w = N <= 128 ? 128 : 256;
+    XS_REQUIRE(make_map(&mx, x, rows_cap, K, ldx, BM), "gemm (tcgen05, grouped): the input's tensor map could not be made");
+    XS_REQUIRE(make_map(&mw, w, (int64_t)E * N, K, K, box_w), "gemm (tcgen05, grouped): the weight's tensor map could not be made");
+    const int rc = box_w == 128 ? launch_grouped<128, 6>(mx, mw, p, meta, max_m_tiles, N, stream)
+                                : launch_grouped<256, 4>(mx, mw, p, meta, max_m_tiles, N, stream);
+    XS_REQUIRE(rc == 0, "gemm (tcgen05, grouped): launch failed: %s", cudaGetErrorString(cudaGetLastError()));
     return 0;
 }

@@ -270,3 +270,338 @@ XS_API int xs_gemm_batched(const void* x, int64_t ldx, int64_t sx, const void* w
     XS_LAUNCH_CHECK("gemm_batched");
     return 0;
 }
+
+// ================================================================================================================
+// The same attention on tensor cores (mma.sync m16n8k16, bfloat16 operands, float32 sums), for prompts and for single
+// tokens alike. A CTA of eight warps owns 64 query rows of one sequence, a row being a (token, head) pair (token-major, so
+// that a tile's rows stand at neighbouring positions and share their keys; in a decode step the rows are the heads of
+// the sequence's one token). It walks the visible keys one cache page (64 positions) at a time: the page's rows
+// [64, R + Dr] come into shared memory by cp.async; warp (wm, wn) forms the scores of rows 16 wm .. 16 wm + 15 with keys
+// 32 wn .. 32 wn + 31 from the query tile in shared memory (ldmatrix), the two warps of a row group exchange their row
+// maxima and their probabilities (bfloat16) through shared memory, and each then adds P V for its half of the R value
+// columns (the values are the first R columns of the same rows, read with ldmatrix.trans). With `splits` > 1 the
+// key pages of a sequence are cut over that many CTAs (single tokens: few rows, long ranges), which leave maximum, sum
+// and unnormalised output per row in scratch for a combine kernel. The sink joins the denominator at the very end.
+namespace {
+
+__device__ __forceinline__ float log2e() { return 1.4426950408889634f; }
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
+struct LatentMmaArgs {
+    const __nv_bfloat16* q_lat;     // (token, head) rows of R, strides qs_t, qs_h
+    int64_t qs_t, qs_h;
+    const __nv_bfloat16* q_rot;     // [T, H, Dr]
+    const __nv_bfloat16* pool;      // [pages, 64, R + Dr]
+    const int32_t* page_table;      // [n_seqs, P]
+    int P;
+    const int32_t* cu_seqlens;      // [n_seqs + 1]
+    const int32_t* kv_lens;         // [n_seqs] keys of each sequence after the step
+    const __nv_bfloat16* gate;      // [T, >= H] logits or null
+    int64_t ld_gate;
+    const float* sink;              // [H] or null
+    __nv_bfloat16* out;             // (token, head) rows of R, strides os_t, os_h
+    int64_t os_t, os_h;
+    float* scratch;                 // splits > 1: [T * H, splits, R + 2] (maximum, sum, output)
+    int H, R, Dr, window, splits;
+    float scale_log2;               // scale * log2(e)
+};
+
+constexpr int kRows = 64, kKeys = 64;
+
+template <int RT>     // value columns a warp owns: up to 64 RT (R <= 128 RT)
+__global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(const LatentMmaArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int W = a.R + a.Dr;
+    const int WP = (W + 15) & ~15;
+    const int ldw = WP + 8;                                  // elements between rows of the query and key tiles
+    __nv_bfloat16* sQ = (__nv_bfloat16*)smem;                // [64][ldw]
+    __nv_bfloat16* sK = sQ + kRows * ldw;                    // [64][ldw]
+    __nv_bfloat16* sP = sK + kKeys * ldw;                    // [4][16][72]
+    float* sRed = (float*)(sP + 4 * 16 * 72);                // [2][64]
+    pdl_launch_dependents();
+    const int seq = blockIdx.y, split = blockIdx.z;
+    const int t0 = a.cu_seqlens[seq], q_len = a.cu_seqlens[seq + 1] - t0, kv_len = a.kv_lens[seq];
+    const int m0 = blockIdx.x * kRows;
+    if (m0 >= q_len * a.H) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wm = warp & 3, wn = warp >> 2;
+    const int first_pos = kv_len - q_len;                    // position of the step's first token
+    const int tok_first = m0 / a.H, tok_last = min(q_len - 1, (m0 + kRows - 1) / a.H);
+    const int j_hi = first_pos + tok_last;
+    const int j_lo = a.window > 0 ? max(0, first_pos + tok_first - a.window + 1) : 0;
+    int b_lo = j_lo / kKeys, b_hi = j_hi / kKeys + 1;        // pages [b_lo, b_hi)
+    if (a.splits > 1) {
+        const int per = (b_hi - b_lo + a.splits - 1) / a.splits;
+        b_lo = b_lo + split * per;
+        b_hi = min(b_hi, b_lo + per);
+    }
+    const int32_t* table = a.page_table + (int64_t)seq * a.P;
+    // zero the padding columns of both tiles once (loads never write them)
+    for (int idx = threadIdx.x; idx < 2 * kRows * (ldw - W); idx += blockDim.x) {
+        const int r = idx / (ldw - W), c = W + idx % (ldw - W);
+        sQ[r * ldw + c] = __float2bfloat16_rn(0.0f);         // (rows 64..127 of this index space are the key tile's)
+    }
+    pdl_wait();
+    // the query tile: row rho -> token rho / H, head rho % H; rows past the sequence's last are zero
+    for (int idx = threadIdx.x; idx < kRows * (W / 8); idx += blockDim.x) {
+        const int r = idx / (W / 8), c = (idx % (W / 8)) * 8;
+        const int rho = m0 + r;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (rho < q_len * a.H) {
+            const int tok = t0 + rho / a.H, h = rho % a.H;
+            v = c < a.R ? *(const uint4*)(a.q_lat + (int64_t)tok * a.qs_t + (int64_t)h * a.qs_h + c)
+                        : *(const uint4*)(a.q_rot + ((int64_t)tok * a.H + h) * a.Dr + (c - a.R));
+        }
+        *(uint4*)(sQ + r * ldw + c) = v;
+    }
+    // this thread's two rows (of the warp's 16) and their positions
+    const int r_lo = wm * 16 + (lane >> 2), r_hi = r_lo + 8;
+    const int rho_lo = m0 + r_lo, rho_hi = m0 + r_hi;
+    const int pos_lo = rho_lo < q_len * a.H ? first_pos + rho_lo / a.H : -1;
+    const int pos_hi = rho_hi < q_len * a.H ? first_pos + rho_hi / a.H : -1;
+    const int min_lo = a.window > 0 ? pos_lo - a.window + 1 : 0, min_hi = a.window > 0 ? pos_hi - a.window + 1 : 0;
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
+    const int ch = ((a.R / 2 + 15) / 16) * 16;               // value columns of a warp
+    const int col0 = wn * ch;
+    const int RP = (a.R + 15) & ~15;
+    float o[8 * RT][4];
+#pragma unroll
+    for (int i = 0; i < 8 * RT; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    const uint32_t sQ_u = (uint32_t)__cvta_generic_to_shared(sQ), sK_u = (uint32_t)__cvta_generic_to_shared(sK);
+    const uint32_t sP_u = (uint32_t)__cvta_generic_to_shared(sP + wm * 16 * 72);
+
+    for (int b = b_lo; b < b_hi; ++b) {
+        __syncthreads();                                     // the last page's values have been read
+        const __nv_bfloat16* page = a.pool + (int64_t)table[b] * kKeys * W;
+        for (int idx = threadIdx.x; idx < kKeys * (W / 8); idx += blockDim.x) {
+            const int r = idx / (W / 8), c = (idx % (W / 8)) * 8;
+            cp_async16(sK_u + (uint32_t)(r * ldw + c) * 2, page + (int64_t)r * W + c);
+        }
+        cp_async_wait_all();
+        __syncthreads();
+        // scores of 16 rows x 32 keys
+        float s[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+        for (int kk = 0; kk < WP; kk += 16) {
+            uint32_t qa[4], kb0[4], kb1[4];
+            ldmatrix_x4(qa, sQ_u + (uint32_t)((wm * 16 + (lane & 15)) * ldw + kk + (lane >> 4) * 8) * 2);
+            const int krow = wn * 32 + (lane & 7) + ((lane >> 4) << 3), kcol = kk + ((lane >> 3) & 1) * 8;
+            ldmatrix_x4(kb0, sK_u + (uint32_t)(krow * ldw + kcol) * 2);
+            ldmatrix_x4(kb1, sK_u + (uint32_t)((krow + 16) * ldw + kcol) * 2);
+            mma_bf16(s[0], qa, kb0[0], kb0[1]);
+            mma_bf16(s[1], qa, kb0[2], kb0[3]);
+            mma_bf16(s[2], qa, kb1[0], kb1[1]);
+            mma_bf16(s[3], qa, kb1[2], kb1[3]);
+        }
+        // scale, mask, this warp's row maxima
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int j = b * kKeys + wn * 32 + nt * 8 + (lane & 3) * 2 + e;
+                s[nt][e] = (j <= pos_lo && j >= min_lo) ? s[nt][e] * a.scale_log2 : -INFINITY;
+                s[nt][2 + e] = (j <= pos_hi && j >= min_hi) ? s[nt][2 + e] * a.scale_log2 : -INFINITY;
+                mx_lo = fmaxf(mx_lo, s[nt][e]);
+                mx_hi = fmaxf(mx_hi, s[nt][2 + e]);
+            }
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        if ((lane & 3) == 0) {
+            sRed[wn * 64 + r_lo] = mx_lo;
+            sRed[wn * 64 + r_hi] = mx_hi;
+        }
+        __syncthreads();
+        const float new_lo = fmaxf(m_lo, fmaxf(sRed[r_lo], sRed[64 + r_lo]));
+        const float new_hi = fmaxf(m_hi, fmaxf(sRed[r_hi], sRed[64 + r_hi]));
+        const float use_lo = new_lo == -INFINITY ? 0.0f : new_lo, use_hi = new_hi == -INFINITY ? 0.0f : new_hi;
+        const float corr_lo = exp2f(m_lo - use_lo), corr_hi = exp2f(m_hi - use_hi);     // 0 while the old maximum is -inf
+        m_lo = new_lo;
+        m_hi = new_hi;
+        l_lo *= corr_lo;
+        l_hi *= corr_hi;
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt) {
+            const float p0 = exp2f(s[nt][0] - use_lo), p1 = exp2f(s[nt][1] - use_lo);
+            const float p2 = exp2f(s[nt][2] - use_hi), p3 = exp2f(s[nt][3] - use_hi);
+            // the sums run over the probabilities as the products see them (rounded to bfloat16)
+            const __nv_bfloat162 v01 = __floats2bfloat162_rn(p0, p1), v23 = __floats2bfloat162_rn(p2, p3);
+            l_lo += __bfloat162float(v01.x) + __bfloat162float(v01.y);
+            l_hi += __bfloat162float(v23.x) + __bfloat162float(v23.y);
+            const int kc = wn * 32 + nt * 8 + (lane & 3) * 2;
+            *(__nv_bfloat162*)(sP + (wm * 16 + (lane >> 2)) * 72 + kc) = v01;
+            *(__nv_bfloat162*)(sP + (wm * 16 + (lane >> 2) + 8) * 72 + kc) = v23;
+        }
+#pragma unroll
+        for (int i = 0; i < 8 * RT; ++i) {
+            o[i][0] *= corr_lo;
+            o[i][1] *= corr_lo;
+            o[i][2] *= corr_hi;
+            o[i][3] *= corr_hi;
+        }
+        __syncthreads();                                     // both halves of P are written
+        // O += P V over this warp's value columns
+#pragma unroll
+        for (int ks = 0; ks < kKeys / 16; ++ks) {
+            uint32_t pa[4];
+            ldmatrix_x4(pa, sP_u + (uint32_t)((lane & 15) * 72 + ks * 16 + (lane >> 4) * 8) * 2);
+#pragma unroll
+            for (int np = 0; np < 4 * RT; ++np) {
+                const int c = col0 + np * 16;
+                if (np * 16 < ch && c < RP) {
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, sK_u + (uint32_t)((ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldw + c + (lane >> 4) * 8) * 2);
+                    mma_bf16(o[2 * np], pa, vb[0], vb[1]);
+                    mma_bf16(o[2 * np + 1], pa, vb[2], vb[3]);
+                }
+            }
+        }
+    }
+    // row sums: over the quad, then over the two warps of the row group
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    __syncthreads();
+    if ((lane & 3) == 0) {
+        sRed[wn * 64 + r_lo] = l_lo;
+        sRed[wn * 64 + r_hi] = l_hi;
+    }
+    __syncthreads();
+    l_lo = sRed[r_lo] + sRed[64 + r_lo];
+    l_hi = sRed[r_hi] + sRed[64 + r_hi];
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int rho = half ? rho_hi : rho_lo;
+        if (rho >= q_len * a.H) continue;
+        const int tok = t0 + rho / a.H, h = rho % a.H;
+        const float m = half ? m_hi : m_lo;
+        float l = half ? l_hi : l_lo;
+        if (a.splits > 1) {
+            float* dst = a.scratch + (((int64_t)tok * a.H + h) * a.splits + split) * (a.R + 2);
+            if (wn == 0 && (lane & 3) == 0) {
+                dst[0] = m;
+                dst[1] = l;
+            }
+#pragma unroll
+            for (int i = 0; i < 8 * RT; ++i) {
+                const int c = col0 + i * 8 + (lane & 3) * 2;
+                if (i * 8 < ch && c < a.R) {
+                    dst[2 + c] = o[i][2 * half];
+                    dst[2 + c + 1] = o[i][2 * half + 1];
+                }
+            }
+            continue;
+        }
+        if (a.sink != nullptr) l += exp2f(a.sink[h] * log2e() - m);
+        float norm = 1.0f / l;
+        if (a.gate != nullptr) norm *= 1.0f / (1.0f + expf(-__bfloat162float(a.gate[(int64_t)tok * a.ld_gate + h])));
+        __nv_bfloat16* dst = a.out + (int64_t)tok * a.os_t + (int64_t)h * a.os_h;
+#pragma unroll
+        for (int i = 0; i < 8 * RT; ++i) {
+            const int c = col0 + i * 8 + (lane & 3) * 2;
+            if (i * 8 < ch && c < a.R)
+                *(__nv_bfloat162*)(dst + c) = __floats2bfloat162_rn(o[i][2 * half] * norm, o[i][2 * half + 1] * norm);
+        }
+    }
+}
+
+// One block per (token, head): the splits' maxima, sums and outputs into the final row.
+__global__ void latent_attention_combine_kernel(const float* __restrict__ scratch, const float* __restrict__ sink,
+                                                const __nv_bfloat16* __restrict__ gate, int64_t ld_gate,
+                                                __nv_bfloat16* __restrict__ out, int64_t os_t, int64_t os_h, int H, int R,
+                                                int splits) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tok = blockIdx.x / H, h = blockIdx.x % H;
+    const float* src = scratch + (int64_t)blockIdx.x * splits * (R + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, src[(int64_t)s * (R + 2)]);
+    float L = 0.0f;
+    for (int s = 0; s < splits; ++s) L += src[(int64_t)s * (R + 2) + 1] * exp2f(src[(int64_t)s * (R + 2)] - M);
+    if (sink != nullptr) L += exp2f(sink[h] * log2e() - M);
+    float norm = 1.0f / L;
+    if (gate != nullptr) norm *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(int64_t)tok * ld_gate + h])));
+    __nv_bfloat16* dst = out + (int64_t)tok * os_t + (int64_t)h * os_h;
+    for (int c = threadIdx.x; c < R; c += blockDim.x) {
+        float v = 0.0f;
+        for (int s = 0; s < splits; ++s) v += src[(int64_t)s * (R + 2) + 2 + c] * exp2f(src[(int64_t)s * (R + 2)] - M);
+        dst[c] = __float2bfloat16_rn(v * norm);
+    }
+}
+
+}  // namespace
+
+XS_API int xs_latent_attention_mma_supports(int R, int Dr, int page_size) {
+    return R >= 16 && R % 8 == 0 && Dr >= 8 && Dr % 8 == 0 && R <= 512 && page_size == 64 &&
+           (size_t)(2 * 64 * (((R + Dr + 15) & ~15) + 8) * 2 + 4 * 16 * 72 * 2 + 2 * 64 * 4) <= 227 * 1024;
+}
+
+XS_API int64_t xs_latent_attention_mma_scratch_bytes(int64_t rows, int R, int splits) {
+    return splits > 1 ? rows * splits * (R + 2) * (int64_t)sizeof(float) : 0;
+}
+
+// max_q_len: the most tokens a sequence brings (the grid's bound); scratch for splits > 1.
+XS_API int xs_latent_attention_mma(const void* q_lat, int64_t qs_t, int64_t qs_h, const void* q_rot, const void* pool,
+                                   const int32_t* page_table, int P, const int32_t* cu_seqlens, const int32_t* kv_lens,
+                                   const void* gate, int64_t ld_gate, const float* sink, void* out, int64_t os_t, int64_t os_h,
+                                   void* scratch, int64_t scratch_bytes, int T, int n_seqs, int max_q_len, int H, int R, int Dr,
+                                   int page_size, float scale, int window, int splits, cudaStream_t stream) {
+    if (T == 0 || n_seqs == 0) return 0;
+    XS_REQUIRE(xs_latent_attention_mma_supports(R, Dr, page_size), "latent attention (mma): rank %d, %d rotated, pages of %d", R, Dr,
+               page_size);
+    XS_REQUIRE(H > 0 && window >= 0 && splits >= 1 && splits <= 65535 && n_seqs <= 65535 && max_q_len > 0,
+               "latent attention (mma): %d heads, window %d, %d splits, %d sequences", H, window, splits, n_seqs);
+    XS_REQUIRE(qs_t % 8 == 0 && qs_h % 8 == 0 && os_t % 2 == 0 && os_h % 2 == 0 && (uintptr_t)q_lat % 16 == 0 &&
+                   (uintptr_t)q_rot % 16 == 0 && (uintptr_t)pool % 16 == 0 && (uintptr_t)out % 4 == 0,
+               "latent attention (mma): operands are not aligned");
+    XS_REQUIRE(splits == 1 || (scratch != nullptr && scratch_bytes >= xs_latent_attention_mma_scratch_bytes((int64_t)T * H, R, splits)),
+               "latent attention (mma): %d splits need %lld bytes of scratch", splits,
+               (long long)xs_latent_attention_mma_scratch_bytes((int64_t)T * H, R, splits));
+    LatentMmaArgs a = {(const __nv_bfloat16*)q_lat, qs_t, qs_h, (const __nv_bfloat16*)q_rot, (const __nv_bfloat16*)pool,
+                       page_table, P, cu_seqlens, kv_lens, (const __nv_bfloat16*)gate, ld_gate, sink, (__nv_bfloat16*)out,
+                       os_t, os_h, (float*)scratch, H, R, Dr, window, splits, scale * 1.4426950408889634f};
+    const int WP = (R + Dr + 15) & ~15;
+    const size_t smem = (size_t)2 * 64 * (WP + 8) * 2 + 4 * 16 * 72 * 2 + 2 * 64 * 4;
+    const dim3 grid(ceil_div_i((int64_t)max_q_len * H, kRows), n_seqs, splits);
+#define XS_GO(RT)                                                                                                       \
+    do {                                                                                                                \
+        static bool opted = false;                                                                                      \
+        if (!opted) {                                                                                                   \
+            cudaFuncSetAttribute(latent_attention_mma_kernel<RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); \
+            opted = true;                                                                                               \
+        }                                                                                                               \
+        xs_launch(latent_attention_mma_kernel<RT>, grid, dim3(256), smem, stream, a);                                   \
+    } while (0)
+    if (R <= 128) XS_GO(1);
+    else if (R <= 256) XS_GO(2);
+    else XS_GO(4);
+#undef XS_GO
+    XS_LAUNCH_CHECK("latent_attention_mma");
+    if (splits > 1) {
+        xs_launch(latent_attention_combine_kernel, dim3(T * H), dim3(128), 0, stream, (const float*)scratch, sink,
+                  (const __nv_bfloat16*)gate, ld_gate, (__nv_bfloat16*)out, os_t, os_h, H, R, splits);
+        XS_LAUNCH_CHECK("latent_attention_combine");
+    }
+    return 0;
+}

@@ -57,12 +57,15 @@ def _signatures(lib) -> None:
         "xs_grouped_rmsnorm": [P, P, P, I, I, I, I, F, P],
         "xs_clamped_glu": [P, P, I, I, I, L, F, F, F, P],
         "xs_moe_route": [P, I, I, I, P, P, P],
-        "xs_moe_plan": [P, I, I, P, P, P, P],
+        "xs_moe_plan": [P, I, I, I, I, P, P, P, P],
+        "xs_moe_gather": [P, L, P, I, P, I, I, P],
+        "xs_gemm_tc_grouped": [P, P, P, I, I, P, I, I, I, I, I, L, L, P, P],
         "xs_moe_gemm": [P, L, P, P, L, P, I, P, I, I, I, I, I, I, P],
         "xs_moe_combine": [P, P, P, P, I, I, I, I, P],
         "xs_latent_prepare": [P, L, P, L, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, I, P],
         "xs_latent_attention_generic": [P, L, L, P, P, P, I, P, P, P, L, P, P, L, L, I, I, I, I, I, F, I, I, P],
         "xs_gemm_batched": [P, L, L, P, L, L, P, L, L, I, I, I, I, I, P],
+        "xs_latent_attention_mma": [P, L, L, P, P, P, I, P, P, P, L, P, P, L, L, P, L, I, I, I, I, I, I, I, F, I, I, P],
         "xs_mamba2_conv": [P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, P],
         "xs_mamba2_scan": [P, P, L, I, P, P, P, P, P, P, P, I, I, I, I, I, I, P],
         "xs_mamba2_scan_chunked": [P, P, L, I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P],
@@ -96,6 +99,12 @@ def _signatures(lib) -> None:
     lib.xs_moe_tile_rows.argtypes = []
     lib.xs_moe_max_tiles.restype = c_int
     lib.xs_moe_max_tiles.argtypes = [c_int, c_int]
+    lib.xs_latent_attention_mma_supports.restype = c_int
+    lib.xs_latent_attention_mma_supports.argtypes = [c_int, c_int, c_int]
+    lib.xs_latent_attention_mma_scratch_bytes.restype = c_int64
+    lib.xs_latent_attention_mma_scratch_bytes.argtypes = [c_int64, c_int, c_int]
+    lib.xs_moe_max_tiles_of.restype = c_int
+    lib.xs_moe_max_tiles_of.argtypes = [c_int, c_int, c_int]
     lib.xs_gemm_small_m_ksplit.restype = c_int
     lib.xs_gemm_small_m_ksplit.argtypes = [c_int, c_int, c_int, c_int]
     lib.xs_gemm_small_m_scratch_bytes.restype = c_int64
@@ -814,15 +823,47 @@ def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, wts: torch.Tens
     _check(load().xs_moe_route(logits.data_ptr(), T, E, int(top), ids.data_ptr(), wts.data_ptr(), _stream()))
 
 
-def moe_plan(ids: torch.Tensor, experts: int, place: torch.Tensor, source: torch.Tensor, meta: torch.Tensor) -> None:
+def moe_max_tiles_of(rows: int, experts: int, tile_rows: int) -> int:
+    """The same for tiles of `tile_rows` rows with every expert's rows padded to whole tiles."""
+    return int(load().xs_moe_max_tiles_of(rows, experts, tile_rows))
+
+
+def moe_plan(ids: torch.Tensor, experts: int, place: torch.Tensor, source: torch.Tensor, meta: torch.Tensor,
+             tile_rows: int = 0) -> None:
     """Sorts the rows (token, choice) by expert: place[row] = its place in that order, source[place] = row, and meta =
-    [tiles, -, -, -, (expert, first place, rows) per tile]."""
+    [tiles, -, -, -, (expert, first place, rows) per tile]. tile_rows > 0: tiles of that many rows and every expert's
+    rows padded to whole tiles (source, which then has tile_rows * moe_max_tiles_of places, is -1 where no row stands)."""
     n = ids.numel()
     for t, name in ((ids, "ids"), (place, "place"), (source, "source"), (meta, "meta")):
         _need(t, name, torch.int32)
-    if place.numel() < n or source.numel() < n or meta.numel() < 4 + 3 * moe_max_tiles(n, experts):
+    tiles = moe_max_tiles_of(n, experts, tile_rows) if tile_rows else moe_max_tiles(n, experts)
+    if place.numel() < n or source.numel() < (tiles * tile_rows if tile_rows else n) or meta.numel() < 4 + 3 * tiles:
         raise KernelError("moe_plan: an output is too small")
-    _check(load().xs_moe_plan(ids.data_ptr(), n, int(experts), place.data_ptr(), source.data_ptr(), meta.data_ptr(), _stream()))
+    _check(load().xs_moe_plan(ids.data_ptr(), n, int(experts), int(tile_rows), source.numel(), place.data_ptr(),
+                              source.data_ptr(), meta.data_ptr(), _stream()))
+
+
+def moe_gather(x: torch.Tensor, source: torch.Tensor, top: int, sorted_rows: torch.Tensor) -> None:
+    """sorted_rows[r] = x[source[r] // top], zeros where source[r] < 0 (bfloat16 rows of a multiple of 8 elements)."""
+    _need(sorted_rows, "sorted rows", torch.bfloat16); _need(source, "source", torch.int32)
+    if x.dtype != torch.bfloat16 or x.stride(1) != 1 or sorted_rows.shape[1] != x.shape[1] or sorted_rows.shape[0] != source.numel():
+        raise KernelError(f"moe_gather: x {tuple(x.shape)}, sorted {tuple(sorted_rows.shape)}, {source.numel()} places")
+    _check(load().xs_moe_gather(x.data_ptr(), x.stride(0), source.data_ptr(), int(top), sorted_rows.data_ptr(),
+                                sorted_rows.shape[0], x.shape[1], _stream()))
+
+
+def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch.Tensor, max_tiles: int, glu: bool) -> None:
+    """out[r] = w[expert of r's tile] . x[r] on tcgen05 tensor cores for the padded row tiles (128 rows) of a plan.
+    w: [experts, N, K] bfloat16; with `glu` each expert's rows come in blocks of 8 gate and 8 up rows and
+    out[r] = silu(gate) * up has N / 2 columns."""
+    _need(x, "x", torch.bfloat16); _need(w, "expert weights", torch.bfloat16); _need(out, "out", torch.bfloat16)
+    E, N, K = w.shape
+    if x.shape[1] != K or out.shape[0] != x.shape[0] or out.shape[1] != (N // 2 if glu else N) or x.shape[0] < 128 * max_tiles:
+        raise KernelError(f"gemm (tcgen05, grouped): x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    mark_bounded(x.device)
+    _check(load().xs_gemm_tc_grouped(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), EPI_SWIGLU if glu else EPI_STORE,
+                                     meta.data_ptr(), int(max_tiles), x.shape[0], E, N, K, x.stride(0), out.stride(0),
+                                     gemm_tc_status(x.device).data_ptr(), _stream()))
 
 
 def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch.Tensor, rows: int, source: Optional[torch.Tensor],
@@ -899,6 +940,43 @@ def latent_attention_generic(q_lat: torch.Tensor, q_rot: torch.Tensor, pool: tor
         q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_rot.data_ptr(), pool.data_ptr(), page_table.data_ptr(),
         page_table.shape[1], seq_of_token.data_ptr(), positions.data_ptr(), _ptr(gate), ld_gate, _ptr(sink), out.data_ptr(),
         out.stride(0), out.stride(1), T, H, R, Dr, page_size, float(scale), int(window), _code(q_lat), _stream()))
+
+
+def latent_attention_mma_supports(rank: int, rot_dim: int, page_size: int) -> bool:
+    return bool(load().xs_latent_attention_mma_supports(rank, rot_dim, page_size))
+
+
+def latent_attention_mma_scratch_bytes(rows: int, rank: int, splits: int) -> int:
+    return int(load().xs_latent_attention_mma_scratch_bytes(rows, rank, splits))
+
+
+def latent_attention_mma(q_lat: torch.Tensor, q_rot: torch.Tensor, pool: torch.Tensor, page_table: torch.Tensor,
+                         cu_seqlens: torch.Tensor, kv_lens: torch.Tensor, gate: Optional[torch.Tensor],
+                         sink: Optional[torch.Tensor], out: torch.Tensor, scratch: Optional[torch.Tensor], n_seqs: int,
+                         max_q_len: int, page_size: int, scale: float, window: int, splits: int) -> None:
+    """Latent attention on tensor cores over the bfloat16 cache. q_lat, out: [T, heads, rank] views; q_rot [T, heads,
+    rot_dim]. With splits > 1 every sequence's key pages are cut over that many CTAs and `scratch` (bytes, at least
+    latent_attention_mma_scratch_bytes(T * heads, rank, splits)) takes their partial results."""
+    T, H, R = q_lat.shape
+    Dr = q_rot.shape[2]
+    _need(q_rot, "q_rot", torch.bfloat16); _need(pool, "cache", torch.bfloat16); _need(page_table, "page table", torch.int32)
+    if q_lat.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or q_lat.stride(2) != 1 or out.stride(2) != 1 or tuple(out.shape) != (T, H, R):
+        raise KernelError(f"latent attention (mma): q {tuple(q_lat.shape)} {q_lat.dtype}, out {tuple(out.shape)} {out.dtype}")
+    if tuple(pool.shape[1:]) != (1, 1, page_size, R + Dr):
+        raise KernelError(f"cache is {tuple(pool.shape)}, expected [*, 1, 1, {page_size}, {R + Dr}]")
+    ld_gate = 0
+    if gate is not None:
+        if gate.dtype != torch.bfloat16 or gate.stride(1) != 1 or gate.shape[0] != T or gate.shape[1] < H:
+            raise KernelError(f"gate is {tuple(gate.shape)} {gate.dtype} for {T} tokens of {H} heads")
+        ld_gate = gate.stride(0)
+    if sink is not None:
+        _need(sink, "sink", torch.float32)
+    _check(load().xs_latent_attention_mma(
+        q_lat.data_ptr(), q_lat.stride(0), q_lat.stride(1), q_rot.data_ptr(), pool.data_ptr(), page_table.data_ptr(),
+        page_table.shape[1], cu_seqlens.data_ptr(), kv_lens.data_ptr(), _ptr(gate), ld_gate, _ptr(sink), out.data_ptr(),
+        out.stride(0), out.stride(1), _ptr(scratch), 0 if scratch is None else scratch.numel() * scratch.element_size(),
+        T, n_seqs, max_q_len, H, R, Dr, page_size, float(scale), int(window), int(splits), _stream()),
+        kernels=2 if splits > 1 else 1)
 
 
 def gemm_batched(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> None:

@@ -8,6 +8,7 @@ RoutedExperts:  `experts` SwiGLU feed-forwards without biases; a token's router 
 """
 from __future__ import annotations
 
+import os
 from typing import Dict
 
 import torch
@@ -62,10 +63,20 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"routed experts: top {spec.top} (at most 16 are supported)")
         self.spec, self.rt = spec, rt
         n = spec.names
-        # [experts, 2 F, hidden] with an expert's gate rows before its up rows, and [experts, hidden, F]
-        self.w_gate_up = rt.matrix(torch.stack([
-            torch.cat([weights[n["gate"].format(e=e)].to(torch.float32), weights[n["up"].format(e=e)].to(torch.float32)], 0)
-            for e in range(spec.experts)]))
+        # [experts, 2 F, hidden] and [experts, hidden, F]. An expert's gate rows stand before its up rows; where the
+        # tcgen05 product runs (bfloat16, widths that are multiples of 8) they stand in blocks of 8 gate rows and the 8
+        # up rows of the same outputs, so that the product's epilogue can apply the activation.
+        F, H = spec.intermediate, spec.hidden
+        self.tensor_cores = (rt.mode == "bfloat16" and F % 8 == 0 and H % 8 == 0
+                             and os.environ.get("XS_EXPERTS_GEMM", "tcgen05") == "tcgen05")
+
+        def stacked(e):
+            g, u = weights[n["gate"].format(e=e)].to(torch.float32), weights[n["up"].format(e=e)].to(torch.float32)
+            if self.tensor_cores:
+                return torch.stack([g.view(F // 8, 8, H), u.view(F // 8, 8, H)], 1).reshape(2 * F, H)
+            return torch.cat([g, u], 0)
+
+        self.w_gate_up = rt.matrix(torch.stack([stacked(e) for e in range(spec.experts)]))
         self.w_down = rt.matrix(torch.stack([weights[n["down"].format(e=e)].to(torch.float32) for e in range(spec.experts)]))
         self.w_router = rt.matrix(weights[n["router"]])
 
@@ -81,12 +92,26 @@ class RoutedExperts(FeedForward):
         source = ws.get("moe_source", (n,), torch.int32)
         meta = ws.get("moe_meta", (4 + 3 * ops.moe_max_tiles(n, s.experts),), torch.int32)
         ops.moe_route(logits, s.top, ids, wts)
+        out = ws.get("ffn_out", (T, s.hidden), rt.act_dtype)
+        if self.tensor_cores:
+            # every expert's rows padded to tiles of 128: gather, two tcgen05 products over the plan's tiles, combine
+            tiles = ops.moe_max_tiles_of(n, s.experts, 128)
+            source = ws.get("moe_source_padded", (128 * tiles,), torch.int32)
+            meta = ws.get("moe_meta_padded", (4 + 3 * tiles,), torch.int32)
+            ops.moe_plan(ids, s.experts, place, source, meta, tile_rows=128)
+            rows_in = ws.get("moe_rows_in", (128 * tiles, s.hidden), rt.act_dtype)
+            ops.moe_gather(y, source, s.top, rows_in)
+            act = ws.get("moe_act", (128 * tiles, s.intermediate), rt.act_dtype)
+            ops.gemm_tc_grouped(rows_in, self.w_gate_up, act, meta, tiles, glu=True)
+            rows_out = ws.get("moe_rows", (128 * tiles, s.hidden), rt.act_dtype)
+            ops.gemm_tc_grouped(act, self.w_down, rows_out, meta, tiles, glu=False)
+            ops.moe_combine(rows_out, place, wts, out, s.top)
+            return out
         ops.moe_plan(ids, s.experts, place, source, meta)
         act = ws.get("moe_act", (n, s.intermediate), rt.act_dtype)
         ops.moe_gemm(y, self.w_gate_up, act, meta, n, source, s.top, glu=True)
         rows_out = ws.get("moe_rows", (n, s.hidden), rt.act_dtype)
         ops.moe_gemm(act, self.w_down, rows_out, meta, n, None, s.top, glu=False)
-        out = ws.get("ffn_out", (T, s.hidden), rt.act_dtype)
         ops.moe_combine(rows_out, place, wts, out, s.top)
         return out
 

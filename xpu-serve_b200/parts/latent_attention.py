@@ -13,6 +13,7 @@ product gives q, d and the gate logits (their weights are stacked at load).
 """
 from __future__ import annotations
 
+import os
 from typing import Dict
 
 import torch
@@ -91,9 +92,31 @@ class LatentAttentionMixer(Mixer):
         rt.batched_product(o_lat, self.w_uv, o.transpose(0, 1))
         return rt.linear(o.view(T, H * s.vdim), self.w_o, "mixer_out")
 
+    def fast_path(self, step) -> bool:
+        """Whether this step's attention runs on tensor cores (bfloat16, sizes in 16-byte pieces, pages of 64)."""
+        s = self.spec
+        return (self.rt.mode == "bfloat16" and os.environ.get("XS_LATENT_ATTENTION", "mma") == "mma"
+                and ops.latent_attention_mma_supports(s.kv_rank, s.rot_dim, step.page_size))
+
     def attend(self, q_lat, q_rot, cache, table, step, gate, o_lat) -> None:
         """q_lat, o_lat: [heads, tokens, kv_rank]."""
-        s = self.spec
+        s, rt = self.spec, self.rt
+        if self.fast_path(step):
+            # A CTA owns 64 (token, head) rows of a sequence. Few tiles facing many keys (single tokens, a short piece
+            # of a long sequence): each sequence's key pages are cut over several CTAs so that every SM streams a part.
+            tiles = -(-step.max_q_len * s.heads // 64) * step.n_seqs
+            blocks = -(-step.max_kv_len // step.page_size)
+            if s.window > 0:
+                blocks = min(blocks, -(-(s.window + step.max_q_len) // step.page_size) + 1)
+            splits = max(1, min(blocks, 64, rt.sm_count // max(tiles, 1)))
+            scratch = None
+            if splits > 1:
+                need = ops.latent_attention_mma_scratch_bytes(q_rot.shape[0] * s.heads, s.kv_rank, splits)
+                scratch = rt.ws.get("lat_scratch", (need,), torch.uint8)
+            ops.latent_attention_mma(q_lat.transpose(0, 1), q_rot, cache.storage, table, step.cu_seqlens, step.kv_lens, gate,
+                                     self.sink, o_lat.transpose(0, 1), scratch, step.n_seqs, step.max_q_len, step.page_size,
+                                     s.scale, s.window, splits)
+            return
         ops.latent_attention_generic(q_lat.transpose(0, 1), q_rot, cache.storage, table, step.seq_of_token, step.positions,
                                      gate, self.sink, o_lat.transpose(0, 1), step.page_size, s.scale, s.window)
 
