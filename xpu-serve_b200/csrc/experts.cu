@@ -34,6 +34,56 @@ __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out
     }
 }
 
+// 8 outputs a thread, 16-byte loads and stores (bfloat16, F a multiple of 8, rows 16-byte aligned).
+__global__ void clamped_glu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int64_t total8,
+                                          int F8, int64_t ld, float limit, float alpha, float shift) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t t = i / F8;
+        const int j = (int)(i - t * F8);
+        const __nv_bfloat16* row = gu + t * ld;
+        const uint4 g = *reinterpret_cast<const uint4*>(row + 8 * j);
+        const uint4 u = *reinterpret_cast<const uint4*>(row + 8 * (int64_t)F8 + 8 * j);
+        const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+        const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
+        uint4 o;
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float2 gf = __bfloat1622float2(gp[k]), uf = __bfloat1622float2(up[k]);
+            gf.x = fminf(gf.x, limit);
+            gf.y = fminf(gf.y, limit);
+            uf.x = fminf(fmaxf(uf.x, -limit), limit);
+            uf.y = fminf(fmaxf(uf.y, -limit), limit);
+            op[k] = __floats2bfloat162_rn(gf.x * sigmoid_f(alpha * gf.x) * (uf.x + shift), gf.y * sigmoid_f(alpha * gf.y) * (uf.y + shift));
+        }
+        *reinterpret_cast<uint4*>(out + t * 8 * (int64_t)F8 + 8 * j) = o;
+    }
+}
+
+// ----------------------------------------------------------------------------------------------------- router logits
+// logits[t, e] = x[t] . w[e] in float32: a block per token keeps the token's row in shared memory (as float32), a warp
+// per expert walks its weight row; a lane's partial sums and the warp's reduction run in an order that depends on K alone.
+template <typename T>
+__global__ void moe_logits_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ w, float* __restrict__ logits,
+                                  int E, int K) {
+    extern __shared__ float xrow[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) xrow[k] = to_f32(x[(int64_t)t * ldx + k]);
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    for (int e = warp; e < E; e += warps) {
+        const T* we = w + (int64_t)e * K;
+        float acc = 0.0f;
+        for (int k = lane; k < K; k += 32) acc = fmaf(xrow[k], to_f32(we[k]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) logits[(int64_t)t * E + e] = acc;
+    }
+}
+
 // ------------------------------------------------------------------------------------------------------------ route
 __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int top, int32_t* __restrict__ ids,
                                  float* __restrict__ wts) {
@@ -241,12 +291,32 @@ XS_API int xs_clamped_glu(const void* gu, void* out, int dtype, int T, int F, in
                           float shift, cudaStream_t stream) {
     if (T == 0) return 0;
     XS_REQUIRE(T > 0 && F > 0 && ld >= 2 * (int64_t)F, "clamped_glu: %d rows, %d columns, stride %lld", T, F, (long long)ld);
+    if (dtype == XS_BF16 && F % 8 == 0 && ld % 8 == 0 && (uintptr_t)gu % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        const int64_t total8 = (int64_t)T * (F / 8);
+        const int blocks8 = (int)((total8 + 255) / 256 < 148 * 32 ? (total8 + 255) / 256 : 148 * 32);
+        xs_launch(clamped_glu_bf16x8_kernel, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
+                  total8, F / 8, ld, limit, alpha, shift);
+        XS_LAUNCH_CHECK("clamped_glu");
+        return 0;
+    }
     const int64_t total = (int64_t)T * F;
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     XS_DISPATCH_DTYPE(dtype, TT,
                       xs_launch(clamped_glu_kernel<TT>, dim3(blocks), dim3(256), 0, stream, (const TT*)gu, (TT*)out, total,
                                 F, ld, limit, alpha, shift));
     XS_LAUNCH_CHECK("clamped_glu");
+    return 0;
+}
+
+XS_API int xs_moe_logits(const void* x, int64_t ldx, const void* w, float* logits, int T, int E, int K, int dtype,
+                         cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(T > 0 && E > 0 && K > 0 && (size_t)K * 4 <= 48 * 1024, "moe_logits: %d tokens, %d experts, width %d (at most 12288)", T, E, K);
+    const int threads = E >= 8 ? 256 : 128;
+    XS_DISPATCH_DTYPE(dtype, TT,
+                      xs_launch(moe_logits_kernel<TT>, dim3(T), dim3(threads), (size_t)K * sizeof(float), stream, (const TT*)x, ldx,
+                                (const TT*)w, logits, E, K));
+    XS_LAUNCH_CHECK("moe_logits");
     return 0;
 }
 

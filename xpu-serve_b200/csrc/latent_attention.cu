@@ -19,7 +19,7 @@
 
 namespace {
 
-constexpr int kMaxRank = 512;     // R of the generic kernel: 16 accumulators a lane
+constexpr int kMaxRank = 1024;    // R of the generic kernel: 32 accumulators a lane
 
 // One block per token: the latent's norm, the rotation of the shared key part and of every head's rotated query part,
 // and the cache write. down: [T, R + Dr]; q: [T, H, Dn + Dr]; q_rot: [T, H, Dr]. The rotation couples channel i with
@@ -218,6 +218,48 @@ gemm_batched_kernel(const T* __restrict__ x, int64_t ldx, int64_t sx, const T* _
     }
 }
 
+// The same product for few rows (M <= 16: single tokens): a weight-streaming kernel. A block keeps x[b] (M x K, float32)
+// in shared memory; each of its warps owns output columns n and walks w[b][n] once, every lane summing its k's for all M
+// rows, then the warp reduces (an order that depends on K alone).
+template <typename T>
+__global__ void __launch_bounds__(256)
+gemm_batched_few_rows_kernel(const T* __restrict__ x, int64_t ldx, int64_t sx, const T* __restrict__ w, int64_t ldw, int64_t sw,
+                             T* __restrict__ out, int64_t ldo, int64_t so, int M, int N, int K, int cols_per_block) {
+    extern __shared__ float xs_rows[];          // [M][K]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int b = blockIdx.y;
+    x += (int64_t)b * sx;
+    w += (int64_t)b * sw;
+    out += (int64_t)b * so;
+    for (int idx = threadIdx.x; idx < M * K; idx += blockDim.x) {
+        const int m = idx / K, k = idx - m * K;
+        xs_rows[idx] = to_f32(x[(int64_t)m * ldx + k]);
+    }
+    __syncthreads();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    const int n_lo = blockIdx.x * cols_per_block, n_hi = min(N, n_lo + cols_per_block);
+    for (int n = n_lo + warp; n < n_hi; n += warps) {
+        const T* wn = w + (int64_t)n * ldw;
+        float acc[16];
+#pragma unroll
+        for (int m = 0; m < 16; ++m) acc[m] = 0.0f;
+        for (int k = lane; k < K; k += 32) {
+            const float wv = to_f32(wn[k]);
+#pragma unroll
+            for (int m = 0; m < 16; ++m)
+                if (m < M) acc[m] = fmaf(xs_rows[m * K + k], wv, acc[m]);
+        }
+#pragma unroll
+        for (int m = 0; m < 16; ++m) {
+            if (m < M) {
+                const float v = warp_sum(acc[m]);
+                if (lane == 0) out[(int64_t)m * ldo + n] = from_f32<T>(v);
+            }
+        }
+    }
+}
+
 }  // namespace
 
 XS_API int xs_latent_prepare(const void* down, int64_t ld_down, const void* q, int64_t ld_q, const float* norm_w,
@@ -262,6 +304,15 @@ XS_API int xs_gemm_batched(const void* x, int64_t ldx, int64_t sx, const void* w
     if (M == 0 || N == 0 || batch == 0) return 0;
     XS_REQUIRE(batch > 0 && batch <= 65535 && M > 0 && N > 0 && K > 0, "gemm_batched: %d x (%d x %d x %d)", batch, M, N, K);
     XS_REQUIRE(ldx >= K && ldw >= K && ldo >= N, "gemm_batched: a row stride is shorter than its row");
+    if (M <= 16 && (size_t)M * K * 4 <= 48 * 1024) {
+        const int cols = 32;        // columns a block owns (8 warps, 4 each)
+        XS_DISPATCH_DTYPE(dtype, TT,
+                          xs_launch(gemm_batched_few_rows_kernel<TT>, dim3(ceil_div_i(N, cols), batch), dim3(256),
+                                    (size_t)M * K * sizeof(float), stream, (const TT*)x, ldx, sx, (const TT*)w, ldw, sw, (TT*)out,
+                                    ldo, so, M, N, K, cols));
+        XS_LAUNCH_CHECK("gemm_batched (few rows)");
+        return 0;
+    }
     const dim3 grid(ceil_div_i(N, BN), ceil_div_i(M, BM), batch);
     XS_REQUIRE(grid.y <= 65535, "gemm_batched: %d rows exceed the grid limit", M);
     XS_DISPATCH_DTYPE(dtype, TT,

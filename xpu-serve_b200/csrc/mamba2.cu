@@ -21,7 +21,7 @@
 
 namespace {
 
-constexpr int kMaxTaps = 8;
+constexpr int kMaxTaps = 16;
 
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
@@ -55,6 +55,43 @@ __global__ void mamba2_conv_kernel(const T* __restrict__ proj, int64_t ld, int c
         acc = fmaf(w[k], v, acc);
     }
     out[(int64_t)t * C + c] = from_f32<T>(silu_f(acc));
+}
+
+// The same for bfloat16 with 8 channels a thread (16-byte loads and stores): C, col0 and ld multiples of 8.
+__global__ void mamba2_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj, int64_t ld, int col0,
+                                          const float* __restrict__ taps_w, const float* __restrict__ bias,
+                                          const __nv_bfloat16* __restrict__ state, const int32_t* __restrict__ seq_of_token,
+                                          const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ slots,
+                                          __nv_bfloat16* __restrict__ out, int Tn, int C, int taps) {
+    pdl_launch_dependents();
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    const int t = blockIdx.x;
+    if (c >= C) return;
+    const int seq = seq_of_token[t];
+    const int local = t - cu_seqlens[seq];
+    const int64_t slot = slots[seq];
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = bias != nullptr ? bias[c + j] : 0.0f;
+    pdl_wait();
+    for (int k = 0; k < taps; ++k) {
+        const int back = taps - 1 - k;
+        const __nv_bfloat16* src = local - back >= 0 ? proj + (int64_t)(t - back) * ld + col0 + c
+                                                      : state + (slot * (taps - 1) + (taps - 1 - (back - local))) * C + c;
+        const uint4 raw = *reinterpret_cast<const uint4*>(src);
+        const __nv_bfloat162* v2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(v2[j]);
+            acc[2 * j] = fmaf(taps_w[(int64_t)(c + 2 * j) * taps + k], f.x, acc[2 * j]);
+            acc[2 * j + 1] = fmaf(taps_w[(int64_t)(c + 2 * j + 1) * taps + k], f.y, acc[2 * j + 1]);
+        }
+    }
+    uint4 o;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(silu_f(acc[2 * j]), silu_f(acc[2 * j + 1]));
+    *reinterpret_cast<uint4*>(out + (int64_t)t * C + c) = o;
 }
 
 // After the convolution: a sequence's state becomes its last taps - 1 inputs (the step's, and the old state's where the
@@ -107,7 +144,7 @@ constexpr int kTok = 16;       // tokens whose B, C, dt and decay are staged in 
 
 template <typename T, int NS, int MODE>
 __global__ void mamba2_scan_kernel(ScanArgs a) {
-    extern __shared__ float sm[];     // B[kTok][N], C[kTok][N], dt[kTok], decay[kTok]
+    extern __shared__ __align__(16) float sm[];     // B[kTok][N], C[kTok][N], dt[kTok], decay[kTok]
     float* sB = sm;
     float* sC = sB + kTok * a.N;
     float* sdt = sC + kTok * a.N;
@@ -134,9 +171,10 @@ __global__ void mamba2_scan_kernel(ScanArgs a) {
     pdl_wait();
     if (n <= 0) return;
     const int rounds = (a.N + NS - 1) / NS;
+    const bool vec4 = (a.N & 3) == 0;
     float* st = MODE == 0 ? a.state + ((int64_t)a.slots[seq] * a.heads + h) * a.N * a.P
                           : a.chunk_state + ((int64_t)unit * a.heads + h) * a.N * a.P;
-    // with more than one round of state rows the outputs are summed over the rounds in shared memory
+    // with more than one round of state rows the outputs are summed over the rounds in the output buffer
     for (int r = 0; r < rounds; ++r) {
         const int n_lo = r * NS;
         float S[NS];
@@ -167,11 +205,33 @@ __global__ void mamba2_scan_kernel(ScanArgs a) {
                 const float* Bt = sB + tt * a.N + n_lo;
                 const float* Ct = sC + tt * a.N + n_lo;
                 float y = 0.0f;
+                if (vec4) {         // N a multiple of 4: B and C four at a time, four partial sums (a short dependency chain)
+                    float y0 = 0.0f, y1 = 0.0f, y2 = 0.0f, y3 = 0.0f;
 #pragma unroll
-                for (int k = 0; k < NS; ++k) {
-                    if (n_lo + k < a.N) {
-                        S[k] = fmaf(da, S[k], dtx * Bt[k]);
-                        y = fmaf(S[k], Ct[k], y);
+                    for (int k = 0; k < NS; k += 4) {
+                        if (n_lo + k < a.N) {
+                            const float4 b4 = *reinterpret_cast<const float4*>(Bt + k);
+                            S[k] = fmaf(da, S[k], dtx * b4.x);
+                            S[k + 1] = fmaf(da, S[k + 1], dtx * b4.y);
+                            S[k + 2] = fmaf(da, S[k + 2], dtx * b4.z);
+                            S[k + 3] = fmaf(da, S[k + 3], dtx * b4.w);
+                            if (MODE != 1) {        // a chunk's first pass wants its end state only
+                                const float4 c4 = *reinterpret_cast<const float4*>(Ct + k);
+                                y0 = fmaf(S[k], c4.x, y0);
+                                y1 = fmaf(S[k + 1], c4.y, y1);
+                                y2 = fmaf(S[k + 2], c4.z, y2);
+                                y3 = fmaf(S[k + 3], c4.w, y3);
+                            }
+                        }
+                    }
+                    y = (y0 + y1) + (y2 + y3);
+                } else {
+#pragma unroll
+                    for (int k = 0; k < NS; ++k) {
+                        if (n_lo + k < a.N) {
+                            S[k] = fmaf(da, S[k], dtx * Bt[k]);
+                            y = fmaf(S[k], Ct[k], y);
+                        }
                     }
                 }
                 total *= da;
@@ -250,9 +310,15 @@ XS_API int xs_mamba2_conv(const void* proj, int64_t ld, int col0, const float* t
     XS_REQUIRE(C > 0 && taps >= 1 && taps <= kMaxTaps, "mamba2_conv: %d channels, %d taps (at most %d)", C, taps, kMaxTaps);
     XS_REQUIRE(n_seqs > 0 && C <= 65535 * 128, "mamba2_conv: %d tokens in %d sequences, %d channels", T, n_seqs, C);
     const int tiles = ceil_div_i(C, 128);
-    XS_DISPATCH_DTYPE(dtype, TT,
-                      xs_launch(mamba2_conv_kernel<TT>, dim3(T, tiles), dim3(128), 0, stream, (const TT*)proj, ld, col0,
-                                taps_w, bias, (const TT*)state, seq_of_token, cu_seqlens, slots, (TT*)out, T, C, taps));
+    if (dtype == XS_BF16 && C % 8 == 0 && col0 % 8 == 0 && ld % 8 == 0 && (uintptr_t)proj % 16 == 0 && (uintptr_t)state % 16 == 0 &&
+        (uintptr_t)out % 16 == 0) {
+        xs_launch(mamba2_conv_bf16x8_kernel, dim3(T, ceil_div_i(C / 8, 128)), dim3(128), 0, stream, (const __nv_bfloat16*)proj, ld,
+                  col0, taps_w, bias, (const __nv_bfloat16*)state, seq_of_token, cu_seqlens, slots, (__nv_bfloat16*)out, T, C, taps);
+    } else {
+        XS_DISPATCH_DTYPE(dtype, TT,
+                          xs_launch(mamba2_conv_kernel<TT>, dim3(T, tiles), dim3(128), 0, stream, (const TT*)proj, ld, col0,
+                                    taps_w, bias, (const TT*)state, seq_of_token, cu_seqlens, slots, (TT*)out, T, C, taps));
+    }
     XS_LAUNCH_CHECK("mamba2_conv");
     if (taps > 1) {
         XS_DISPATCH_DTYPE(dtype, TT,

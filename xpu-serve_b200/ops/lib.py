@@ -57,6 +57,7 @@ def _signatures(lib) -> None:
         "xs_grouped_rmsnorm": [P, P, P, I, I, I, I, F, P],
         "xs_clamped_glu": [P, P, I, I, I, L, F, F, F, P],
         "xs_moe_route": [P, I, I, I, P, P, P],
+        "xs_moe_logits": [P, L, P, P, I, I, I, I, P],
         "xs_moe_plan": [P, I, I, I, I, P, P, P, P],
         "xs_moe_gather": [P, L, P, I, P, I, I, P],
         "xs_gemm_tc_grouped": [P, P, P, I, I, P, I, I, I, I, I, L, L, P, P],
@@ -812,6 +813,16 @@ def clamped_glu(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float,
 def moe_max_tiles(rows: int, experts: int) -> int:
     """The most row tiles that `rows` rows over `experts` experts can make (what the products' grids are sized by)."""
     return int(load().xs_moe_max_tiles(rows, experts))
+
+
+def moe_logits(x: torch.Tensor, w: torch.Tensor, logits: torch.Tensor) -> None:
+    """logits[t, e] = x[t] . w[e], float32 sums (not rounded) of the products of x's and w's element type."""
+    _need(w, "router weight", x.dtype); _need(logits, "router logits", torch.float32)
+    T, K = x.shape
+    E = w.shape[0]
+    if x.stride(1) != 1 or w.shape[1] != K or tuple(logits.shape) != (T, E):
+        raise KernelError(f"moe_logits: x {tuple(x.shape)}, w {tuple(w.shape)}, logits {tuple(logits.shape)}")
+    _check(load().xs_moe_logits(x.data_ptr(), x.stride(0), w.data_ptr(), logits.data_ptr(), T, E, K, _code(x), _stream()))
 
 
 def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, wts: torch.Tensor) -> None:

@@ -44,8 +44,8 @@ class Mamba2Mixer(Mixer):
                 StateNeed((spec.heads, spec.state, spec.vdim), "float32"))
 
     def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
-        if not 1 <= spec.taps <= 8:
-            raise ValueError(f"mamba2: {spec.taps} taps (1 to 8 are supported)")
+        if not 1 <= spec.taps <= 16:
+            raise ValueError(f"mamba2: {spec.taps} taps (1 to 16 are supported)")
         self.spec, self.rt = spec, rt
         n = spec.names
         self.w_in = rt.matrix(weights[n["in"]])
