@@ -424,6 +424,7 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(const Late
     // this thread's two rows (of the warp's 16) and their positions
     const int r_lo = wm * 16 + (lane >> 2), r_hi = r_lo + 8;
     const int rho_lo = m0 + r_lo, rho_hi = m0 + r_hi;
+    const bool active = m0 + wm * 16 < q_len * a.H;          // single tokens with few heads fill one row group only
     const int pos_lo = rho_lo < q_len * a.H ? first_pos + rho_lo / a.H : -1;
     const int pos_hi = rho_hi < q_len * a.H ? first_pos + rho_hi / a.H : -1;
     const int min_lo = a.window > 0 ? pos_lo - a.window + 1 : 0, min_hi = a.window > 0 ? pos_hi - a.window + 1 : 0;
@@ -450,7 +451,7 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(const Late
         float s[4][4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
-        for (int kk = 0; kk < WP; kk += 16) {
+        for (int kk = 0; active && kk < WP; kk += 16) {      // (a row group past the sequence's rows has nothing to add)
             uint32_t qa[4], kb0[4], kb1[4];
             ldmatrix_x4(qa, sQ_u + (uint32_t)((wm * 16 + (lane & 15)) * ldw + kk + (lane >> 4) * 8) * 2);
             const int krow = wn * 32 + (lane & 7) + ((lane >> 4) << 3), kcol = kk + ((lane >> 3) & 1) * 8;
@@ -514,6 +515,7 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(const Late
         // O += P V over this warp's value columns
 #pragma unroll
         for (int ks = 0; ks < kKeys / 16; ++ks) {
+            if (!active) break;
             uint32_t pa[4];
             ldmatrix_x4(pa, sP_u + (uint32_t)((lane & 15) * 72 + ks * 16 + (lane >> 4) * 8) * 2);
 #pragma unroll

@@ -17,6 +17,8 @@
 // and writes the outputs.
 #include <math.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace {
@@ -73,8 +75,14 @@ __global__ void mamba2_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = bias != nullptr ? bias[c + j] : 0.0f;
+    float wv[32];                                   // the 8 channels' taps, contiguous in memory (taps <= 4 here)
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+        if (i < 2 * taps) *reinterpret_cast<float4*>(wv + 4 * i) = *reinterpret_cast<const float4*>(taps_w + (int64_t)c * taps + 4 * i);
     pdl_wait();
-    for (int k = 0; k < taps; ++k) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        if (k >= taps) break;
         const int back = taps - 1 - k;
         const __nv_bfloat16* src = local - back >= 0 ? proj + (int64_t)(t - back) * ld + col0 + c
                                                       : state + (slot * (taps - 1) + (taps - 1 - (back - local))) * C + c;
@@ -83,8 +91,8 @@ __global__ void mamba2_conv_bf16x8_kernel(const __nv_bfloat16* __restrict__ proj
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const float2 f = __bfloat1622float2(v2[j]);
-            acc[2 * j] = fmaf(taps_w[(int64_t)(c + 2 * j) * taps + k], f.x, acc[2 * j]);
-            acc[2 * j + 1] = fmaf(taps_w[(int64_t)(c + 2 * j + 1) * taps + k], f.y, acc[2 * j + 1]);
+            acc[2 * j] = fmaf(wv[(2 * j) * taps + k], f.x, acc[2 * j]);
+            acc[2 * j + 1] = fmaf(wv[(2 * j + 1) * taps + k], f.y, acc[2 * j + 1]);
         }
     }
     uint4 o;
@@ -149,6 +157,8 @@ __global__ void mamba2_scan_kernel(ScanArgs a) {
     float* sC = sB + kTok * a.N;
     float* sdt = sC + kTok * a.N;
     float* sda = sdt + kTok;
+    float* sX = sda + kTok;                         // x[kTok][threads]
+    float* sY = sX + kTok * blockDim.x;             // y[kTok][threads]: a thread's own outputs until the chunk's tokens are done
     pdl_launch_dependents();
     const int h = blockIdx.x, unit = blockIdx.y;
     const int p = threadIdx.x;
@@ -172,6 +182,8 @@ __global__ void mamba2_scan_kernel(ScanArgs a) {
     if (n <= 0) return;
     const int rounds = (a.N + NS - 1) / NS;
     const bool vec4 = (a.N & 3) == 0;
+    // rows of B, C and x in whole 16-byte pieces (bfloat16)
+    const bool vec8 = (a.N & 7) == 0 && (a.P & 7) == 0 && (a.C & 7) == 0 && (reinterpret_cast<uintptr_t>(a.xbc) & 15) == 0;
     float* st = MODE == 0 ? a.state + ((int64_t)a.slots[seq] * a.heads + h) * a.N * a.P
                           : a.chunk_state + ((int64_t)unit * a.heads + h) * a.N * a.P;
     // with more than one round of state rows the outputs are summed over the rounds in the output buffer
@@ -185,11 +197,58 @@ __global__ void mamba2_scan_kernel(ScanArgs a) {
         for (int c0 = 0; c0 < n; c0 += kTok) {
             const int cnt = min(kTok, n - c0);
             __syncthreads();
-            for (int idx = threadIdx.x; idx < cnt * a.N; idx += blockDim.x) {
-                const int tt = idx / a.N, k = idx - tt * a.N;
-                const int64_t row = (int64_t)(t0 + c0 + tt) * a.C;
-                sB[tt * a.N + k] = to_f32(xbc[row + inner + g * a.N + k]);
-                sC[tt * a.N + k] = to_f32(xbc[row + inner + (a.G + g) * a.N + k]);
+            bool staged = false;
+            if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+                if (vec8) {
+                    // 16-byte loads, four of B and four of C in flight a thread before anything is stored
+                    const int per_row = a.N >> 3, total8 = cnt * per_row;
+                    for (int base = 0; base < total8; base += 4 * blockDim.x) {
+                        uint4 rb[4], rc[4];
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int idx = base + u * blockDim.x + threadIdx.x;
+                            if (idx < total8) {
+                                const int tt = idx / per_row, kk = idx - tt * per_row;
+                                const T* src = xbc + (int64_t)(t0 + c0 + tt) * a.C + inner + g * a.N + kk * 8;
+                                rb[u] = *reinterpret_cast<const uint4*>(src);
+                                rc[u] = *reinterpret_cast<const uint4*>(src + a.G * a.N);
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const int idx = base + u * blockDim.x + threadIdx.x;
+                            if (idx < total8) {
+                                const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&rb[u]);
+                                const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&rc[u]);
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    *reinterpret_cast<float2*>(sB + idx * 8 + 2 * j) = __bfloat1622float2(b2[j]);
+                                    *reinterpret_cast<float2*>(sC + idx * 8 + 2 * j) = __bfloat1622float2(c2[j]);
+                                }
+                            }
+                        }
+                    }
+                    const int per_x = a.P >> 3, total_x = cnt * per_x;
+                    for (int idx = threadIdx.x; idx < total_x; idx += blockDim.x) {
+                        const int tt = idx / per_x, pp = (idx - tt * per_x) * 8;
+                        const uint4 raw = *reinterpret_cast<const uint4*>(xbc + (int64_t)(t0 + c0 + tt) * a.C + h * a.P + pp);
+                        const __nv_bfloat162* x2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            *reinterpret_cast<float2*>(sX + tt * blockDim.x + pp + 2 * j) = __bfloat1622float2(x2[j]);
+                    }
+                    staged = true;
+                }
+            }
+            if (!staged) {
+                for (int tt = 0; tt < cnt; ++tt) {
+                    const int64_t row = (int64_t)(t0 + c0 + tt) * a.C;
+                    for (int k = threadIdx.x; k < a.N; k += blockDim.x) {
+                        sB[tt * a.N + k] = to_f32(xbc[row + inner + g * a.N + k]);
+                        sC[tt * a.N + k] = to_f32(xbc[row + inner + (a.G + g) * a.N + k]);
+                    }
+                    for (int pp = threadIdx.x; pp < a.P; pp += blockDim.x) sX[tt * blockDim.x + pp] = to_f32(xbc[row + h * a.P + pp]);
+                }
             }
             for (int tt = threadIdx.x; tt < cnt; tt += blockDim.x) {
                 const float dt = softplus_f(to_f32(proj[(int64_t)(t0 + c0 + tt) * a.ld + a.dt_col + h]) + bias);
@@ -198,9 +257,9 @@ __global__ void mamba2_scan_kernel(ScanArgs a) {
             }
             __syncthreads();
             if (!live) continue;
+            // the recurrence over the staged tokens reads shared memory only; outputs wait in sY
             for (int tt = 0; tt < cnt; ++tt) {
-                const int64_t t = t0 + c0 + tt;
-                const float x = to_f32(xbc[t * a.C + h * a.P + p]);
+                const float x = sX[tt * blockDim.x + p];
                 const float da = sda[tt], dtx = sdt[tt] * x;
                 const float* Bt = sB + tt * a.N + n_lo;
                 const float* Ct = sC + tt * a.N + n_lo;
@@ -235,18 +294,26 @@ __global__ void mamba2_scan_kernel(ScanArgs a) {
                     }
                 }
                 total *= da;
-                if (MODE != 1) {
-                    float* yo = a.y + t * inner + h * a.P + p;
-                    if (rounds == 1) {
-                        const float z = to_f32(proj[t * a.ld + h * a.P + p]);
-                        *yo = fmaf(dskip, x, y) * silu_f(z);
-                    } else if (r == 0) {
-                        *yo = y;
-                    } else if (r < rounds - 1) {
-                        *yo += y;
-                    } else {
-                        const float z = to_f32(proj[t * a.ld + h * a.P + p]);
-                        *yo = fmaf(dskip, x, *yo + y) * silu_f(z);
+                sY[tt * blockDim.x + p] = y;
+            }
+            if (MODE != 1) {
+                // the gate's loads of the staged tokens are independent of one another: four in flight at a time
+                for (int t4 = 0; t4 < cnt; t4 += 4) {
+                    float zv[4];
+                    const bool last = rounds == 1 || r == rounds - 1;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                        zv[u] = (last && t4 + u < cnt) ? to_f32(proj[(int64_t)(t0 + c0 + t4 + u) * a.ld + h * a.P + p]) : 0.0f;
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        const int tt = t4 + u;
+                        if (tt >= cnt) break;
+                        const float x = sX[tt * blockDim.x + p], y = sY[tt * blockDim.x + p];
+                        float* yo = a.y + (int64_t)(t0 + c0 + tt) * inner + h * a.P + p;
+                        if (rounds == 1) *yo = fmaf(dskip, x, y) * silu_f(zv[u]);
+                        else if (r == 0) *yo = y;
+                        else if (!last) *yo += y;
+                        else *yo = fmaf(dskip, x, *yo + y) * silu_f(zv[u]);
                     }
                 }
             }
@@ -271,7 +338,7 @@ __global__ void mamba2_carry_kernel(float* __restrict__ state, float* __restrict
     const int c_lo = first_chunk[seq], c_hi = first_chunk[seq + 1];
     float* st = state + ((int64_t)slots[seq] * heads + h) * NP;
     pdl_wait();
-    for (int64_t i = threadIdx.x; i < NP; i += blockDim.x) {
+    for (int64_t i = (int64_t)blockIdx.z * blockDim.x + threadIdx.x; i < NP; i += (int64_t)gridDim.z * blockDim.x) {
         float S = st[i];
         for (int c = c_lo; c < c_hi; ++c) {
             float* cs = chunk_state + ((int64_t)c * heads + h) * NP + i;
@@ -286,7 +353,7 @@ __global__ void mamba2_carry_kernel(float* __restrict__ state, float* __restrict
 template <typename T, int MODE>
 int launch_scan(const ScanArgs& a, int units, cudaStream_t stream) {
     const int threads = ((a.P + 31) / 32) * 32;
-    const size_t smem = (size_t)(2 * kTok * a.N + 2 * kTok) * sizeof(float);
+    const size_t smem = (size_t)(2 * kTok * a.N + 2 * kTok + 2 * kTok * threads) * sizeof(float);
     if (smem > 48 * 1024) {
         xs_set_error("mamba2_scan: a state of %d rows does not fit shared memory", a.N);
         return -1;
@@ -310,7 +377,7 @@ XS_API int xs_mamba2_conv(const void* proj, int64_t ld, int col0, const float* t
     XS_REQUIRE(C > 0 && taps >= 1 && taps <= kMaxTaps, "mamba2_conv: %d channels, %d taps (at most %d)", C, taps, kMaxTaps);
     XS_REQUIRE(n_seqs > 0 && C <= 65535 * 128, "mamba2_conv: %d tokens in %d sequences, %d channels", T, n_seqs, C);
     const int tiles = ceil_div_i(C, 128);
-    if (dtype == XS_BF16 && C % 8 == 0 && col0 % 8 == 0 && ld % 8 == 0 && (uintptr_t)proj % 16 == 0 && (uintptr_t)state % 16 == 0 &&
+    if (dtype == XS_BF16 && taps <= 4 && (uintptr_t)taps_w % 16 == 0 && C % 8 == 0 && col0 % 8 == 0 && ld % 8 == 0 && (uintptr_t)proj % 16 == 0 && (uintptr_t)state % 16 == 0 &&
         (uintptr_t)out % 16 == 0) {
         xs_launch(mamba2_conv_bf16x8_kernel, dim3(T, ceil_div_i(C / 8, 128)), dim3(128), 0, stream, (const __nv_bfloat16*)proj, ld,
                   col0, taps_w, bias, (const __nv_bfloat16*)state, seq_of_token, cu_seqlens, slots, (__nv_bfloat16*)out, T, C, taps);
@@ -360,8 +427,8 @@ XS_API int xs_mamba2_scan_chunked(const void* xbc, const void* proj, int64_t ld,
                   chunk_seq, heads, P, N, G, heads * P + 2 * G * N, 0};
     XS_DISPATCH_DTYPE(dtype, TT, launch_scan<TT, 1>(a, chunks, stream));
     XS_LAUNCH_CHECK("mamba2_scan (chunk states)");
-    xs_launch(mamba2_carry_kernel, dim3(heads, n_seqs), dim3(256), 0, stream, state, chunk_state, chunk_decay, first_chunk,
-              slots, heads, (int64_t)N * P);
+    xs_launch(mamba2_carry_kernel, dim3(heads, n_seqs, ceil_div_i((int64_t)N * P, 256) < 64 ? ceil_div_i((int64_t)N * P, 256) : 64),
+              dim3(256), 0, stream, state, chunk_state, chunk_decay, first_chunk, slots, heads, (int64_t)N * P);
     XS_LAUNCH_CHECK("mamba2_scan (carry)");
     XS_DISPATCH_DTYPE(dtype, TT, launch_scan<TT, 2>(a, chunks, stream));
     XS_LAUNCH_CHECK("mamba2_scan (outputs)");
