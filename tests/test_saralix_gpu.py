@@ -197,7 +197,8 @@ def test_latent_attention_kernel_with_planted_keys(kernel, dtype, window, sink, 
     torch.manual_seed(5)
     H, R, Dr, page = 3, 40, 8, 64
     lens = [300, 129, 64, 1]                    # keys of each sequence after the step
-    q_lens = [5, 1, 1, 1]                       # the step's tokens: a piece of 5 and three single tokens
+    # the step's tokens: a piece of 5 and three single tokens; with key splits, single tokens alone (the small tile)
+    q_lens = [1, 1, 1, 1] if "split" in kernel else [5, 1, 1, 1]
     n_pages = sum(-(-n // page) for n in lens)
     order = torch.randperm(n_pages + 3)
     pool = torch.zeros(n_pages + 4, 1, 1, page, R + Dr, dtype=dtype, device="cuda")
@@ -215,7 +216,7 @@ def test_latent_attention_kernel_with_planted_keys(kernel, dtype, window, sink, 
     for s, (n, q) in enumerate(zip(lens, q_lens)):
         positions += list(range(n - q, n)); seq_of += [s] * q
     # plant: for the last token of sequence 0 (position 299) and the token of sequence 1 (position 128)
-    for s, t in ((0, 4), (1, 5)):
+    for s, t in ((0, q_lens[0] - 1), (1, q_lens[0])):
         pos = positions[t]
         for j in {3, 63, 64, pos - window + 1 if window else 7, pos - window if window else 9} - {-1}:
             if 0 <= j <= pos:
@@ -293,6 +294,7 @@ def test_routed_products_on_tensor_cores(tokens, experts, top, width, ff):
     w_down = (torch.randn(experts, width, ff, generator=g) * 0.2).bfloat16()
     logits = torch.randn(tokens, experts, generator=g)
     logits[:, 1] -= 50.0                                    # an expert that nobody chooses
+    logits[::3, 2] = logits[::3, 0]                         # equal logits: the lower index goes first
     n = tokens * top
     dev = "cuda"
     ids = torch.empty(n, dtype=torch.int32, device=dev)

@@ -14,6 +14,7 @@
 namespace {
 
 constexpr int kMaxTop = 16;
+constexpr int kLocalExperts = 64;
 
 __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf(-z)); }
 
@@ -63,25 +64,42 @@ __global__ void clamped_glu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, 
 }
 
 // ----------------------------------------------------------------------------------------------------- router logits
-// logits[t, e] = x[t] . w[e] in float32: a block per token keeps the token's row in shared memory (as float32), a warp
-// per expert walks its weight row; a lane's partial sums and the warp's reduction run in an order that depends on K alone.
+// logits[t, e] = x[t] . w[e] in float32: a warp per (token, expert) pair walks both rows (16-byte loads where the rows
+// allow, eight loads in flight a lane); a lane's partial sums and the warp's reduction run in an order that depends on
+// K alone, whatever else is in the batch.
 template <typename T>
 __global__ void moe_logits_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ w, float* __restrict__ logits,
-                                  int E, int K) {
-    extern __shared__ float xrow[];
+                                  int Tn, int E, int K, int vec) {
     pdl_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int64_t pair = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (pair >= (int64_t)Tn * E) return;
+    const int t = (int)(pair / E), e = (int)(pair % E);
+    const T* xr = x + (int64_t)t * ldx;
+    const T* we = w + (int64_t)e * K;
     pdl_wait();
-    const int t = blockIdx.x;
-    for (int k = threadIdx.x; k < K; k += blockDim.x) xrow[k] = to_f32(x[(int64_t)t * ldx + k]);
-    __syncthreads();
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    for (int e = warp; e < E; e += warps) {
-        const T* we = w + (int64_t)e * K;
-        float acc = 0.0f;
-        for (int k = lane; k < K; k += 32) acc = fmaf(xrow[k], to_f32(we[k]), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) logits[(int64_t)t * E + e] = acc;
+    float acc = 0.0f;
+    if (vec) {          // bfloat16 rows in whole 16-byte pieces
+        const uint4* x8 = reinterpret_cast<const uint4*>(xr);
+        const uint4* w8 = reinterpret_cast<const uint4*>(we);
+#pragma unroll 4
+        for (int i = lane; i < (K >> 3); i += 32) {
+            const uint4 a = x8[i], b = w8[i];
+            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+            const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 af = __bfloat1622float2(a2[j]), bf = __bfloat1622float2(b2[j]);
+                acc = fmaf(af.x, bf.x, acc);
+                acc = fmaf(af.y, bf.y, acc);
+            }
+        }
+    } else {
+#pragma unroll 8
+        for (int k = lane; k < K; k += 32) acc = fmaf(to_f32(xr[k]), to_f32(we[k]), acc);
     }
+    acc = warp_sum(acc);
+    if (lane == 0) logits[pair] = acc;
 }
 
 // ------------------------------------------------------------------------------------------------------------ route
@@ -91,7 +109,12 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
     pdl_wait();
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= T) return;
-    const float* z = logits + (int64_t)t * E;
+    const float* zg = logits + (int64_t)t * E;
+    float zl[kLocalExperts];            // up to 64 logits are read once, all loads in flight
+    if (E <= kLocalExperts) {
+#pragma unroll
+        for (int e = 0; e < kLocalExperts; ++e) zl[e] = e < E ? zg[e] : 0.0f;
+    }
     int chosen[kMaxTop];
     float val[kMaxTop];
     for (int k = 0; k < top; ++k) {
@@ -101,7 +124,7 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
             bool taken = false;
             for (int j = 0; j < k; ++j) taken |= chosen[j] == e;
             if (taken) continue;
-            const float v = z[e];
+            const float v = E <= kLocalExperts ? zl[e] : zg[e];
             if (best < 0 || v > bv) {
                 best = e;
                 bv = v;
@@ -119,6 +142,58 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
     for (int k = 0; k < top; ++k) {
         ids[(int64_t)t * top + k] = chosen[k];
         wts[(int64_t)t * top + k] = val[k] / sum;
+    }
+}
+
+// A warp per token (E <= 256): a lane holds logits lane, lane + 32, ...; each of the `top` rounds finds the largest logit
+// left (ties: the lower index) by a reduction over the warp.
+__global__ void moe_route_warp_kernel(const float* __restrict__ logits, int T, int E, int top, int32_t* __restrict__ ids,
+                                      float* __restrict__ wts) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= T) return;
+    const float* z = logits + (int64_t)t * E;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = lane + 32 * j < E ? z[lane + 32 * j] : -INFINITY;
+    float mine = 0.0f, largest = 0.0f, sum = 0.0f;
+    int mine_id = 0;
+    for (int k = 0; k < top; ++k) {
+        float bv = -INFINITY;
+        int bi = 1 << 30;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int e = lane + 32 * j;
+            if (e < E && (v[j] > bv || (v[j] == bv && e < bi))) {
+                bv = v[j];
+                bi = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) {
+                bv = ov;
+                bi = oi;
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (lane + 32 * j == bi) v[j] = -INFINITY;       // taken (a logit of -inf itself is never chosen twice: its index is)
+        if (k == 0) largest = bv;
+        const float p = expf(bv - largest);
+        sum += p;
+        if (lane == k) {
+            mine = p;
+            mine_id = bi;
+        }
+    }
+    if (lane < top) {
+        ids[(int64_t)t * top + lane] = mine_id;
+        wts[(int64_t)t * top + lane] = mine / sum;
     }
 }
 
@@ -311,11 +386,11 @@ XS_API int xs_clamped_glu(const void* gu, void* out, int dtype, int T, int F, in
 XS_API int xs_moe_logits(const void* x, int64_t ldx, const void* w, float* logits, int T, int E, int K, int dtype,
                          cudaStream_t stream) {
     if (T == 0) return 0;
-    XS_REQUIRE(T > 0 && E > 0 && K > 0 && (size_t)K * 4 <= 48 * 1024, "moe_logits: %d tokens, %d experts, width %d (at most 12288)", T, E, K);
-    const int threads = E >= 8 ? 256 : 128;
+    XS_REQUIRE(T > 0 && E > 0 && K > 0, "moe_logits: %d tokens, %d experts, width %d", T, E, K);
+    const int vec = dtype == XS_BF16 && K % 8 == 0 && ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0;
     XS_DISPATCH_DTYPE(dtype, TT,
-                      xs_launch(moe_logits_kernel<TT>, dim3(T), dim3(threads), (size_t)K * sizeof(float), stream, (const TT*)x, ldx,
-                                (const TT*)w, logits, E, K));
+                      xs_launch(moe_logits_kernel<TT>, dim3(ceil_div_i((int64_t)T * E, 4)), dim3(128), 0, stream, (const TT*)x, ldx,
+                                (const TT*)w, logits, T, E, K, vec));
     XS_LAUNCH_CHECK("moe_logits");
     return 0;
 }
@@ -324,7 +399,10 @@ XS_API int xs_moe_route(const float* logits, int T, int E, int top, int32_t* ids
     if (T == 0) return 0;
     XS_REQUIRE(T > 0 && E > 0 && top > 0 && top <= E && top <= kMaxTop, "moe_route: %d tokens, %d experts, top %d (at most %d)",
                T, E, top, kMaxTop);
-    xs_launch(moe_route_kernel, dim3(ceil_div_i(T, 128)), dim3(128), 0, stream, logits, T, E, top, ids, wts);
+    if (E <= 256 && E > top)
+        xs_launch(moe_route_warp_kernel, dim3(ceil_div_i(T, 4)), dim3(128), 0, stream, logits, T, E, top, ids, wts);
+    else
+        xs_launch(moe_route_kernel, dim3(ceil_div_i(T, 32)), dim3(32), 0, stream, logits, T, E, top, ids, wts);
     XS_LAUNCH_CHECK("moe_route");
     return 0;
 }

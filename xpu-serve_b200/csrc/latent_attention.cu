@@ -232,9 +232,10 @@ gemm_batched_few_rows_kernel(const T* __restrict__ x, int64_t ldx, int64_t sx, c
     x += (int64_t)b * sx;
     w += (int64_t)b * sw;
     out += (int64_t)b * so;
-    for (int idx = threadIdx.x; idx < M * K; idx += blockDim.x) {
-        const int m = idx / K, k = idx - m * K;
-        xs_rows[idx] = to_f32(x[(int64_t)m * ldx + k]);
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+#pragma unroll
+        for (int m = 0; m < 16; ++m)
+            if (m < M) xs_rows[m * K + k] = to_f32(x[(int64_t)m * ldx + k]);
     }
     __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
@@ -244,11 +245,19 @@ gemm_batched_few_rows_kernel(const T* __restrict__ x, int64_t ldx, int64_t sx, c
         float acc[16];
 #pragma unroll
         for (int m = 0; m < 16; ++m) acc[m] = 0.0f;
-        for (int k = lane; k < K; k += 32) {
-            const float wv = to_f32(wn[k]);
+        for (int k0 = lane; k0 < K; k0 += 128) {           // four weights in flight a lane
+            float wv[4];
 #pragma unroll
-            for (int m = 0; m < 16; ++m)
-                if (m < M) acc[m] = fmaf(xs_rows[m * K + k], wv, acc[m]);
+            for (int u = 0; u < 4; ++u) wv[u] = k0 + 32 * u < K ? to_f32(wn[k0 + 32 * u]) : 0.0f;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int k = k0 + 32 * u;
+                if (k < K) {
+#pragma unroll
+                    for (int m = 0; m < 16; ++m)
+                        if (m < M) acc[m] = fmaf(xs_rows[m * K + k], wv[u], acc[m]);
+                }
+            }
         }
 #pragma unroll
         for (int m = 0; m < 16; ++m) {
@@ -305,7 +314,7 @@ XS_API int xs_gemm_batched(const void* x, int64_t ldx, int64_t sx, const void* w
     XS_REQUIRE(batch > 0 && batch <= 65535 && M > 0 && N > 0 && K > 0, "gemm_batched: %d x (%d x %d x %d)", batch, M, N, K);
     XS_REQUIRE(ldx >= K && ldw >= K && ldo >= N, "gemm_batched: a row stride is shorter than its row");
     if (M <= 16 && (size_t)M * K * 4 <= 48 * 1024) {
-        const int cols = 32;        // columns a block owns (8 warps, 4 each)
+        const int cols = 8;         // columns a block owns (8 warps, one each)
         XS_DISPATCH_DTYPE(dtype, TT,
                           xs_launch(gemm_batched_few_rows_kernel<TT>, dim3(ceil_div_i(N, cols), batch), dim3(256),
                                     (size_t)M * K * sizeof(float), stream, (const TT*)x, ldx, sx, (const TT*)w, ldw, sw, (TT*)out,
@@ -372,9 +381,10 @@ struct LatentMmaArgs {
     float* scratch;                 // splits > 1: [T * H, splits, R + 2] (maximum, sum, output)
     int H, R, Dr, window, splits;
     float scale_log2;               // scale * log2(e)
+    int qrows;                      // query rows a CTA owns: 64, or 16 when no sequence brings more (smaller tile, two CTAs an SM)
 };
 
-constexpr int kRows = 64, kKeys = 64;
+constexpr int kKeys = 64;      // keys a step: one cache page
 
 template <int RT>     // value columns a warp owns: up to 64 RT (R <= 128 RT)
 __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(const LatentMmaArgs a) {
@@ -382,18 +392,20 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(const Late
     const int W = a.R + a.Dr;
     const int WP = (W + 15) & ~15;
     const int ldw = WP + 8;                                  // elements between rows of the query and key tiles
-    __nv_bfloat16* sQ = (__nv_bfloat16*)smem;                // [64][ldw]
-    __nv_bfloat16* sK = sQ + kRows * ldw;                    // [64][ldw]
+    __nv_bfloat16* sQ = (__nv_bfloat16*)smem;                // [qrows][ldw]
+    __nv_bfloat16* sK = sQ + a.qrows * ldw;                  // [64][ldw]
     __nv_bfloat16* sP = sK + kKeys * ldw;                    // [4][16][72]
     float* sRed = (float*)(sP + 4 * 16 * 72);                // [2][64]
     pdl_launch_dependents();
     const int seq = blockIdx.y, split = blockIdx.z;
     const int t0 = a.cu_seqlens[seq], q_len = a.cu_seqlens[seq + 1] - t0, kv_len = a.kv_lens[seq];
-    const int m0 = blockIdx.x * kRows;
+    const int m0 = blockIdx.x * a.qrows;
     if (m0 >= q_len * a.H) return;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wm = warp & 3, wn = warp >> 2;
+    // eight warps: row group wm of four, key / column half wn; the 16-row tile of single tokens runs with two warps (wm 0)
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int wm = a.qrows == 16 ? 0 : warp & 3, wn = a.qrows == 16 ? warp : warp >> 2;
     const int first_pos = kv_len - q_len;                    // position of the step's first token
-    const int tok_first = m0 / a.H, tok_last = min(q_len - 1, (m0 + kRows - 1) / a.H);
+    const int tok_first = m0 / a.H, tok_last = min(q_len - 1, (m0 + a.qrows - 1) / a.H);
     const int j_hi = first_pos + tok_last;
     const int j_lo = a.window > 0 ? max(0, first_pos + tok_first - a.window + 1) : 0;
     int b_lo = j_lo / kKeys, b_hi = j_hi / kKeys + 1;        // pages [b_lo, b_hi)
@@ -404,13 +416,13 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(const Late
     }
     const int32_t* table = a.page_table + (int64_t)seq * a.P;
     // zero the padding columns of both tiles once (loads never write them)
-    for (int idx = threadIdx.x; idx < 2 * kRows * (ldw - W); idx += blockDim.x) {
+    for (int idx = threadIdx.x; idx < (a.qrows + kKeys) * (ldw - W); idx += blockDim.x) {
         const int r = idx / (ldw - W), c = W + idx % (ldw - W);
-        sQ[r * ldw + c] = __float2bfloat16_rn(0.0f);         // (rows 64..127 of this index space are the key tile's)
+        sQ[r * ldw + c] = __float2bfloat16_rn(0.0f);         // (rows from qrows on in this index space are the key tile's)
     }
     pdl_wait();
     // the query tile: row rho -> token rho / H, head rho % H; rows past the sequence's last are zero
-    for (int idx = threadIdx.x; idx < kRows * (W / 8); idx += blockDim.x) {
+    for (int idx = threadIdx.x; idx < a.qrows * (W / 8); idx += blockDim.x) {
         const int r = idx / (W / 8), c = (idx % (W / 8)) * 8;
         const int rho = m0 + r;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -424,7 +436,7 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(const Late
     // this thread's two rows (of the warp's 16) and their positions
     const int r_lo = wm * 16 + (lane >> 2), r_hi = r_lo + 8;
     const int rho_lo = m0 + r_lo, rho_hi = m0 + r_hi;
-    const bool active = m0 + wm * 16 < q_len * a.H;          // single tokens with few heads fill one row group only
+    const bool active = wm * 16 < a.qrows && m0 + wm * 16 < q_len * a.H;      // single tokens with few heads fill one row group only
     const int pos_lo = rho_lo < q_len * a.H ? first_pos + rho_lo / a.H : -1;
     const int pos_hi = rho_hi < q_len * a.H ? first_pos + rho_hi / a.H : -1;
     const int min_lo = a.window > 0 ? pos_lo - a.window + 1 : 0, min_hi = a.window > 0 ? pos_hi - a.window + 1 : 0;
@@ -586,19 +598,33 @@ __global__ void latent_attention_combine_kernel(const float* __restrict__ scratc
                                                 int splits) {
     pdl_launch_dependents();
     pdl_wait();
+    __shared__ float weight[64];      // of each split: 2^(its maximum - the row's), then divided by the row's sum
+    __shared__ float norm_sm;
     const int tok = blockIdx.x / H, h = blockIdx.x % H;
     const float* src = scratch + (int64_t)blockIdx.x * splits * (R + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, src[(int64_t)s * (R + 2)]);
-    float L = 0.0f;
-    for (int s = 0; s < splits; ++s) L += src[(int64_t)s * (R + 2) + 1] * exp2f(src[(int64_t)s * (R + 2)] - M);
-    if (sink != nullptr) L += exp2f(sink[h] * log2e() - M);
-    float norm = 1.0f / L;
-    if (gate != nullptr) norm *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(int64_t)tok * ld_gate + h])));
+    if (threadIdx.x < 32) {           // splits <= 64: two per lane, all loads in flight at once
+        const int s0 = threadIdx.x, s1 = threadIdx.x + 32;
+        const float m0 = s0 < splits ? src[(int64_t)s0 * (R + 2)] : -INFINITY, m1 = s1 < splits ? src[(int64_t)s1 * (R + 2)] : -INFINITY;
+        const float l0 = s0 < splits ? src[(int64_t)s0 * (R + 2) + 1] : 0.0f, l1 = s1 < splits ? src[(int64_t)s1 * (R + 2) + 1] : 0.0f;
+        const float M = warp_max(fmaxf(m0, m1));
+        const float w0 = exp2f(m0 - M), w1 = exp2f(m1 - M);
+        float L = warp_sum(l0 * w0 + l1 * w1);
+        if (sink != nullptr) L += exp2f(sink[h] * log2e() - M);
+        weight[s0] = w0;
+        weight[s1] = w1;
+        if (threadIdx.x == 0) {
+            float norm = 1.0f / L;
+            if (gate != nullptr) norm *= 1.0f / (1.0f + expf(-__bfloat162float(gate[(int64_t)tok * ld_gate + h])));
+            norm_sm = norm;
+        }
+    }
+    __syncthreads();
+    const float norm = norm_sm;
     __nv_bfloat16* dst = out + (int64_t)tok * os_t + (int64_t)h * os_h;
     for (int c = threadIdx.x; c < R; c += blockDim.x) {
         float v = 0.0f;
-        for (int s = 0; s < splits; ++s) v += src[(int64_t)s * (R + 2) + 2 + c] * exp2f(src[(int64_t)s * (R + 2)] - M);
+#pragma unroll 8
+        for (int s = 0; s < splits; ++s) v = fmaf(src[(int64_t)s * (R + 2) + 2 + c], weight[s], v);
         dst[c] = __float2bfloat16_rn(v * norm);
     }
 }
@@ -608,6 +634,15 @@ __global__ void latent_attention_combine_kernel(const float* __restrict__ scratc
 XS_API int xs_latent_attention_mma_supports(int R, int Dr, int page_size) {
     return R >= 16 && R % 8 == 0 && Dr >= 8 && Dr % 8 == 0 && R <= 512 && page_size == 64 &&
            (size_t)(2 * 64 * (((R + Dr + 15) & ~15) + 8) * 2 + 4 * 16 * 72 * 2 + 2 * 64 * 4) <= 227 * 1024;
+}
+
+// Query rows a CTA owns, and how many such CTAs fit an SM (what the key splits of single tokens are sized by).
+XS_API int xs_latent_attention_mma_rows(int max_q_len, int H) { return (int64_t)max_q_len * H <= 16 ? 16 : 64; }
+XS_API int xs_latent_attention_mma_ctas_per_sm(int max_q_len, int H, int R, int Dr) {
+    const int WP = (R + Dr + 15) & ~15;
+    const size_t smem = (size_t)(xs_latent_attention_mma_rows(max_q_len, H) + 64) * (WP + 8) * 2 + 4 * 16 * 72 * 2 + 2 * 64 * 4 + 1024;
+    const int fit = (int)((227 * 1024) / smem);
+    return fit < 1 ? 1 : fit > 2 ? 2 : fit;
 }
 
 XS_API int64_t xs_latent_attention_mma_scratch_bytes(int64_t rows, int R, int splits) {
@@ -633,10 +668,11 @@ XS_API int xs_latent_attention_mma(const void* q_lat, int64_t qs_t, int64_t qs_h
                (long long)xs_latent_attention_mma_scratch_bytes((int64_t)T * H, R, splits));
     LatentMmaArgs a = {(const __nv_bfloat16*)q_lat, qs_t, qs_h, (const __nv_bfloat16*)q_rot, (const __nv_bfloat16*)pool,
                        page_table, P, cu_seqlens, kv_lens, (const __nv_bfloat16*)gate, ld_gate, sink, (__nv_bfloat16*)out,
-                       os_t, os_h, (float*)scratch, H, R, Dr, window, splits, scale * 1.4426950408889634f};
+                       os_t, os_h, (float*)scratch, H, R, Dr, window, splits, scale * 1.4426950408889634f,
+                       xs_latent_attention_mma_rows(max_q_len, H)};
     const int WP = (R + Dr + 15) & ~15;
-    const size_t smem = (size_t)2 * 64 * (WP + 8) * 2 + 4 * 16 * 72 * 2 + 2 * 64 * 4;
-    const dim3 grid(ceil_div_i((int64_t)max_q_len * H, kRows), n_seqs, splits);
+    const size_t smem = (size_t)(a.qrows + 64) * (WP + 8) * 2 + 4 * 16 * 72 * 2 + 2 * 64 * 4;
+    const dim3 grid(ceil_div_i((int64_t)max_q_len * H, a.qrows), n_seqs, splits);
 #define XS_GO(RT)                                                                                                       \
     do {                                                                                                                \
         static bool opted = false;                                                                                      \
@@ -644,7 +680,7 @@ XS_API int xs_latent_attention_mma(const void* q_lat, int64_t qs_t, int64_t qs_h
             cudaFuncSetAttribute(latent_attention_mma_kernel<RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); \
             opted = true;                                                                                               \
         }                                                                                                               \
-        xs_launch(latent_attention_mma_kernel<RT>, grid, dim3(256), smem, stream, a);                                   \
+        xs_launch(latent_attention_mma_kernel<RT>, grid, dim3(a.qrows == 16 ? 64 : 256), smem, stream, a);                                   \
     } while (0)
     if (R <= 128) XS_GO(1);
     else if (R <= 256) XS_GO(2);

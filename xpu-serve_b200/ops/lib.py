@@ -102,6 +102,8 @@ def _signatures(lib) -> None:
     lib.xs_moe_max_tiles.argtypes = [c_int, c_int]
     lib.xs_latent_attention_mma_supports.restype = c_int
     lib.xs_latent_attention_mma_supports.argtypes = [c_int, c_int, c_int]
+    lib.xs_latent_attention_mma_ctas_per_sm.restype = c_int
+    lib.xs_latent_attention_mma_ctas_per_sm.argtypes = [c_int, c_int, c_int, c_int]
     lib.xs_latent_attention_mma_scratch_bytes.restype = c_int64
     lib.xs_latent_attention_mma_scratch_bytes.argtypes = [c_int64, c_int, c_int]
     lib.xs_moe_max_tiles_of.restype = c_int
@@ -955,6 +957,12 @@ def latent_attention_generic(q_lat: torch.Tensor, q_rot: torch.Tensor, pool: tor
 
 def latent_attention_mma_supports(rank: int, rot_dim: int, page_size: int) -> bool:
     return bool(load().xs_latent_attention_mma_supports(rank, rot_dim, page_size))
+
+
+def latent_attention_mma_ctas_per_sm(max_q_len: int, heads: int, rank: int, rot_dim: int) -> int:
+    """CTAs of the kernel that share an SM for steps of at most `max_q_len` tokens a sequence (the tile of single tokens
+    with few heads is smaller)."""
+    return int(load().xs_latent_attention_mma_ctas_per_sm(max_q_len, heads, rank, rot_dim))
 
 
 def latent_attention_mma_scratch_bytes(rows: int, rank: int, splits: int) -> int:

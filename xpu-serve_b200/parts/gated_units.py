@@ -85,10 +85,7 @@ class RoutedExperts(FeedForward):
         T, n = y.shape[0], y.shape[0] * s.top
         ws = rt.ws
         logits = ws.get("moe_logits", (T, s.experts), torch.float32)
-        if s.hidden <= 12288:
-            ops.moe_logits(y, self.w_router, logits)        # float32 sums of the activation type's products, not rounded
-        else:
-            ops.gemm_generic(y, self.w_router, logits)
+        ops.moe_logits(y, self.w_router, logits)            # float32 sums of the activation type's products, not rounded
         ids = ws.get("moe_ids", (n,), torch.int32)
         wts = ws.get("moe_wts", (n,), torch.float32)
         place = ws.get("moe_place", (n,), torch.int32)

@@ -104,11 +104,13 @@ class LatentAttentionMixer(Mixer):
         if self.fast_path(step):
             # A CTA owns 64 (token, head) rows of a sequence. Few tiles facing many keys (single tokens, a short piece
             # of a long sequence): each sequence's key pages are cut over several CTAs so that every SM streams a part.
-            tiles = -(-step.max_q_len * s.heads // 64) * step.n_seqs
+            rows = 16 if step.max_q_len * s.heads <= 16 else 64
+            tiles = -(-step.max_q_len * s.heads // rows) * step.n_seqs
+            slots = rt.sm_count * ops.latent_attention_mma_ctas_per_sm(step.max_q_len, s.heads, s.kv_rank, s.rot_dim)
             blocks = -(-step.max_kv_len // step.page_size)
             if s.window > 0:
                 blocks = min(blocks, -(-(s.window + step.max_q_len) // step.page_size) + 1)
-            splits = max(1, min(blocks, 64, rt.sm_count // max(tiles, 1)))
+            splits = max(1, min(blocks, 64, slots // max(tiles, 1)))
             scratch = None
             if splits > 1:
                 need = ops.latent_attention_mma_scratch_bytes(q_rot.shape[0] * s.heads, s.kv_rank, splits)
