@@ -186,6 +186,7 @@ def plain_latent_attention(q_lat, q_rot, rows, pos, scale, window, sink, gate):
 
 
 @pytest.mark.parametrize("kernel,dtype", [("generic", torch.float32), ("generic", torch.bfloat16), ("mma", torch.bfloat16),
+                                          ("mma few rows", torch.bfloat16), ("mma few rows split", torch.bfloat16),
                                           ("mma split", torch.bfloat16)])
 @pytest.mark.parametrize("window,sink,gate", [(0, False, True), (37, True, False), (64, True, True), (1, True, False)])
 def test_latent_attention_kernel_with_planted_keys(kernel, dtype, window, sink, gate):
@@ -197,8 +198,9 @@ def test_latent_attention_kernel_with_planted_keys(kernel, dtype, window, sink, 
     torch.manual_seed(5)
     H, R, Dr, page = 3, 40, 8, 64
     lens = [300, 129, 64, 1]                    # keys of each sequence after the step
-    # the step's tokens: a piece of 5 and three single tokens; with key splits, single tokens alone (the small tile)
-    q_lens = [1, 1, 1, 1] if "split" in kernel else [5, 1, 1, 1]
+    # the step's tokens: a piece and three single tokens. 12 x 3 heads take the tensor-core kernel of 64-row tiles, 5 x 3 and
+    # single tokens alone the kernel of 16-row tiles
+    q_lens = [1, 1, 1, 1] if kernel == "mma few rows split" else [5, 1, 1, 1] if kernel == "mma few rows" else [12, 1, 1, 1]
     n_pages = sum(-(-n // page) for n in lens)
     order = torch.randperm(n_pages + 3)
     pool = torch.zeros(n_pages + 4, 1, 1, page, R + Dr, dtype=dtype, device="cuda")

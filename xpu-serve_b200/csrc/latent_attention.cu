@@ -381,7 +381,7 @@ struct LatentMmaArgs {
     float* scratch;                 // splits > 1: [T * H, splits, R + 2] (maximum, sum, output)
     int H, R, Dr, window, splits;
     float scale_log2;               // scale * log2(e)
-    int qrows;                      // query rows a CTA owns: 64, or 16 when no sequence brings more (smaller tile, two CTAs an SM)
+    int qrows;                      // query rows a CTA owns: 64, or 16 (the kernel of single tokens) when no sequence brings more than 32
 };
 
 constexpr int kKeys = 64;      // keys a step: one cache page
@@ -401,9 +401,7 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(const Late
     const int t0 = a.cu_seqlens[seq], q_len = a.cu_seqlens[seq + 1] - t0, kv_len = a.kv_lens[seq];
     const int m0 = blockIdx.x * a.qrows;
     if (m0 >= q_len * a.H) return;
-    // eight warps: row group wm of four, key / column half wn; the 16-row tile of single tokens runs with two warps (wm 0)
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int wm = a.qrows == 16 ? 0 : warp & 3, wn = a.qrows == 16 ? warp : warp >> 2;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, wm = warp & 3, wn = warp >> 2;
     const int first_pos = kv_len - q_len;                    // position of the step's first token
     const int tok_first = m0 / a.H, tok_last = min(q_len - 1, (m0 + a.qrows - 1) / a.H);
     const int j_hi = first_pos + tok_last;
@@ -591,6 +589,199 @@ __global__ void __launch_bounds__(256, 1) latent_attention_mma_kernel(const Late
     }
 }
 
+// Single tokens (at most 32 query rows a sequence): 16 rows a CTA, all eight warps on them. Warp w forms the scores of
+// keys 8 w .. 8 w + 7 of the page (two accumulators over alternate k steps), the warps exchange row maxima and the
+// probabilities through shared memory, and warp w then adds P V for its eighth of the value columns. A CTA holds 103 KB
+// of shared memory at 576 channels a row, so two share an SM and a sequence's pages are cut over twice as many CTAs.
+__global__ void __launch_bounds__(256, 2) latent_attention_mma16_kernel(const LatentMmaArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int W = a.R + a.Dr;
+    const int WP = (W + 15) & ~15;
+    const int ldw = WP + 8;
+    __nv_bfloat16* sQ = (__nv_bfloat16*)smem;                // [16][ldw]
+    __nv_bfloat16* sK = sQ + 16 * ldw;                       // [64][ldw]
+    __nv_bfloat16* sP = sK + kKeys * ldw;                    // [16][72]
+    float* sRed = (float*)(sP + 16 * 72);                    // [8][16]
+    pdl_launch_dependents();
+    const int seq = blockIdx.y, split = blockIdx.z;
+    const int t0 = a.cu_seqlens[seq], q_len = a.cu_seqlens[seq + 1] - t0, kv_len = a.kv_lens[seq];
+    const int m0 = blockIdx.x * 16;
+    if (m0 >= q_len * a.H) return;
+    const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int first_pos = kv_len - q_len;
+    const int tok_first = m0 / a.H, tok_last = min(q_len - 1, (m0 + 15) / a.H);
+    const int j_hi = first_pos + tok_last;
+    const int j_lo = a.window > 0 ? max(0, first_pos + tok_first - a.window + 1) : 0;
+    int b_lo = j_lo / kKeys, b_hi = j_hi / kKeys + 1;
+    if (a.splits > 1) {
+        const int per = (b_hi - b_lo + a.splits - 1) / a.splits;
+        b_lo = b_lo + split * per;
+        b_hi = min(b_hi, b_lo + per);
+    }
+    const int32_t* table = a.page_table + (int64_t)seq * a.P;
+    for (int idx = threadIdx.x; idx < (16 + kKeys) * (ldw - W); idx += blockDim.x) {
+        const int r = idx / (ldw - W), c = W + idx % (ldw - W);
+        sQ[r * ldw + c] = __float2bfloat16_rn(0.0f);
+    }
+    pdl_wait();
+    for (int idx = threadIdx.x; idx < 16 * (W / 8); idx += blockDim.x) {
+        const int r = idx / (W / 8), c = (idx % (W / 8)) * 8;
+        const int rho = m0 + r;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (rho < q_len * a.H) {
+            const int tok = t0 + rho / a.H, h = rho % a.H;
+            v = c < a.R ? *(const uint4*)(a.q_lat + (int64_t)tok * a.qs_t + (int64_t)h * a.qs_h + c)
+                        : *(const uint4*)(a.q_rot + ((int64_t)tok * a.H + h) * a.Dr + (c - a.R));
+        }
+        *(uint4*)(sQ + r * ldw + c) = v;
+    }
+    const int r_lo = lane >> 2, r_hi = r_lo + 8;
+    const int rho_lo = m0 + r_lo, rho_hi = m0 + r_hi;
+    const int pos_lo = rho_lo < q_len * a.H ? first_pos + rho_lo / a.H : -1;
+    const int pos_hi = rho_hi < q_len * a.H ? first_pos + rho_hi / a.H : -1;
+    const int min_lo = a.window > 0 ? pos_lo - a.window + 1 : 0, min_hi = a.window > 0 ? pos_hi - a.window + 1 : 0;
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
+    const int cw = (((a.R + 7) / 8 + 15) / 16) * 16;         // value columns of a warp
+    const int col0 = w * cw;
+    const int RP = (a.R + 15) & ~15;
+    float o[8][4];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    const uint32_t sQ_u = (uint32_t)__cvta_generic_to_shared(sQ), sK_u = (uint32_t)__cvta_generic_to_shared(sK);
+    const uint32_t sP_u = (uint32_t)__cvta_generic_to_shared(sP);
+
+    for (int b = b_lo; b < b_hi; ++b) {
+        __syncthreads();
+        const __nv_bfloat16* page = a.pool + (int64_t)table[b] * kKeys * W;
+        for (int r = w; r < kKeys; r += 8)                   // a warp a row: no division on the way
+            for (int c = lane * 8; c < W; c += 256) cp_async16(sK_u + (uint32_t)(r * ldw + c) * 2, page + (int64_t)r * W + c);
+        cp_async_wait_all();
+        __syncthreads();
+        float s0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, s1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        for (int kk = 0; kk < WP; kk += 32) {
+            uint32_t qa[4], kb[4];
+            ldmatrix_x4(kb, sK_u + (uint32_t)((w * 8 + (lane & 7)) * ldw + kk + (lane >> 3) * 8) * 2);
+            ldmatrix_x4(qa, sQ_u + (uint32_t)((lane & 15) * ldw + kk + (lane >> 4) * 8) * 2);
+            mma_bf16(s0, qa, kb[0], kb[1]);
+            if (kk + 16 < WP) {
+                ldmatrix_x4(qa, sQ_u + (uint32_t)((lane & 15) * ldw + kk + 16 + (lane >> 4) * 8) * 2);
+                mma_bf16(s1, qa, kb[2], kb[3]);
+            }
+        }
+        float sc[4];
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int j = b * kKeys + w * 8 + (lane & 3) * 2 + e;
+            sc[e] = (j <= pos_lo && j >= min_lo) ? (s0[e] + s1[e]) * a.scale_log2 : -INFINITY;
+            sc[2 + e] = (j <= pos_hi && j >= min_hi) ? (s0[2 + e] + s1[2 + e]) * a.scale_log2 : -INFINITY;
+            mx_lo = fmaxf(mx_lo, sc[e]);
+            mx_hi = fmaxf(mx_hi, sc[2 + e]);
+        }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        if ((lane & 3) == 0) {
+            sRed[w * 16 + r_lo] = mx_lo;
+            sRed[w * 16 + r_hi] = mx_hi;
+        }
+        __syncthreads();
+        float new_lo = m_lo, new_hi = m_hi;
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+            new_lo = fmaxf(new_lo, sRed[x * 16 + r_lo]);
+            new_hi = fmaxf(new_hi, sRed[x * 16 + r_hi]);
+        }
+        const float use_lo = new_lo == -INFINITY ? 0.0f : new_lo, use_hi = new_hi == -INFINITY ? 0.0f : new_hi;
+        const float corr_lo = exp2f(m_lo - use_lo), corr_hi = exp2f(m_hi - use_hi);
+        m_lo = new_lo;
+        m_hi = new_hi;
+        {
+            const __nv_bfloat162 v01 = __floats2bfloat162_rn(exp2f(sc[0] - use_lo), exp2f(sc[1] - use_lo));
+            const __nv_bfloat162 v23 = __floats2bfloat162_rn(exp2f(sc[2] - use_hi), exp2f(sc[3] - use_hi));
+            l_lo = l_lo * corr_lo + __bfloat162float(v01.x) + __bfloat162float(v01.y);
+            l_hi = l_hi * corr_hi + __bfloat162float(v23.x) + __bfloat162float(v23.y);
+            const int kc = w * 8 + (lane & 3) * 2;
+            *(__nv_bfloat162*)(sP + r_lo * 72 + kc) = v01;
+            *(__nv_bfloat162*)(sP + r_hi * 72 + kc) = v23;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            o[i][0] *= corr_lo;
+            o[i][1] *= corr_lo;
+            o[i][2] *= corr_hi;
+            o[i][3] *= corr_hi;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < kKeys / 16; ++ks) {
+            uint32_t pa[4];
+            ldmatrix_x4(pa, sP_u + (uint32_t)((lane & 15) * 72 + ks * 16 + (lane >> 4) * 8) * 2);
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                const int c = col0 + np * 16;
+                if (np * 16 < cw && c < RP) {
+                    uint32_t vb[4];
+                    ldmatrix_x4_trans(vb, sK_u + (uint32_t)((ks * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ldw + c + (lane >> 4) * 8) * 2);
+                    mma_bf16(o[2 * np], pa, vb[0], vb[1]);
+                    mma_bf16(o[2 * np + 1], pa, vb[2], vb[3]);
+                }
+            }
+        }
+    }
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    __syncthreads();
+    if ((lane & 3) == 0) {
+        sRed[w * 16 + r_lo] = l_lo;
+        sRed[w * 16 + r_hi] = l_hi;
+    }
+    __syncthreads();
+    l_lo = l_hi = 0.0f;
+#pragma unroll
+    for (int x = 0; x < 8; ++x) {
+        l_lo += sRed[x * 16 + r_lo];
+        l_hi += sRed[x * 16 + r_hi];
+    }
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int rho = half ? rho_hi : rho_lo;
+        if (rho >= q_len * a.H) continue;
+        const int tok = t0 + rho / a.H, h = rho % a.H;
+        const float m = half ? m_hi : m_lo;
+        float l = half ? l_hi : l_lo;
+        if (a.splits > 1) {
+            float* dst = a.scratch + (((int64_t)tok * a.H + h) * a.splits + split) * (a.R + 2);
+            if (w == 0 && (lane & 3) == 0) {
+                dst[0] = m;
+                dst[1] = l;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int c = col0 + i * 8 + (lane & 3) * 2;
+                if (i * 8 < cw && c < a.R) {
+                    dst[2 + c] = o[i][2 * half];
+                    dst[2 + c + 1] = o[i][2 * half + 1];
+                }
+            }
+            continue;
+        }
+        if (a.sink != nullptr) l += exp2f(a.sink[h] * log2e() - m);
+        float norm = 1.0f / l;
+        if (a.gate != nullptr) norm *= 1.0f / (1.0f + expf(-__bfloat162float(a.gate[(int64_t)tok * a.ld_gate + h])));
+        __nv_bfloat16* dst = a.out + (int64_t)tok * a.os_t + (int64_t)h * a.os_h;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int c = col0 + i * 8 + (lane & 3) * 2;
+            if (i * 8 < cw && c < a.R)
+                *(__nv_bfloat162*)(dst + c) = __floats2bfloat162_rn(o[i][2 * half] * norm, o[i][2 * half + 1] * norm);
+        }
+    }
+}
+
 // One block per (token, head): the splits' maxima, sums and outputs into the final row.
 __global__ void latent_attention_combine_kernel(const float* __restrict__ scratch, const float* __restrict__ sink,
                                                 const __nv_bfloat16* __restrict__ gate, int64_t ld_gate,
@@ -637,7 +828,7 @@ XS_API int xs_latent_attention_mma_supports(int R, int Dr, int page_size) {
 }
 
 // Query rows a CTA owns, and how many such CTAs fit an SM (what the key splits of single tokens are sized by).
-XS_API int xs_latent_attention_mma_rows(int max_q_len, int H) { return (int64_t)max_q_len * H <= 16 ? 16 : 64; }
+XS_API int xs_latent_attention_mma_rows(int max_q_len, int H) { return (int64_t)max_q_len * H <= 32 ? 16 : 64; }
 XS_API int xs_latent_attention_mma_ctas_per_sm(int max_q_len, int H, int R, int Dr) {
     const int WP = (R + Dr + 15) & ~15;
     const size_t smem = (size_t)(xs_latent_attention_mma_rows(max_q_len, H) + 64) * (WP + 8) * 2 + 4 * 16 * 72 * 2 + 2 * 64 * 4 + 1024;
@@ -680,9 +871,17 @@ XS_API int xs_latent_attention_mma(const void* q_lat, int64_t qs_t, int64_t qs_h
             cudaFuncSetAttribute(latent_attention_mma_kernel<RT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024); \
             opted = true;                                                                                               \
         }                                                                                                               \
-        xs_launch(latent_attention_mma_kernel<RT>, grid, dim3(a.qrows == 16 ? 64 : 256), smem, stream, a);                                   \
+        xs_launch(latent_attention_mma_kernel<RT>, grid, dim3(256), smem, stream, a);                                   \
     } while (0)
-    if (R <= 128) XS_GO(1);
+    if (a.qrows == 16) {
+        static bool opted16 = false;
+        if (!opted16) {
+            cudaFuncSetAttribute(latent_attention_mma16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            opted16 = true;
+        }
+        const size_t smem16 = (size_t)(16 + 64) * (WP + 8) * 2 + 16 * 72 * 2 + 8 * 16 * 4;
+        xs_launch(latent_attention_mma16_kernel, grid, dim3(256), smem16, stream, a);
+    } else if (R <= 128) XS_GO(1);
     else if (R <= 256) XS_GO(2);
     else XS_GO(4);
 #undef XS_GO
