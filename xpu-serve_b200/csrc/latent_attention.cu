@@ -74,6 +74,94 @@ __global__ void latent_prepare_kernel(const T* __restrict__ down, int64_t ld_dow
     }
 }
 
+// The same for bfloat16 rows in whole 16-byte pieces (R, Dr, Dn multiples of 8, dims a multiple of 16): a thread moves 8
+// channels at a time, a rotation's two partner pieces together.
+__device__ __forceinline__ void unpack8(const uint4& raw, float (&v)[8]) {
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(h2[j]);
+        v[2 * j] = f.x;
+        v[2 * j + 1] = f.y;
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&v)[8]) {
+    uint4 o;
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h2[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+    return o;
+}
+// dst[i..i+8) and dst[i + half..) from src's two pieces, turned by cs[i..i+8) (cos, sin)
+__device__ __forceinline__ void rotate_pieces(const __nv_bfloat16* src, __nv_bfloat16* dst, const float2* cs, int i, int half) {
+    float lo[8], hi[8], a[8], b[8];
+    unpack8(*reinterpret_cast<const uint4*>(src + i), lo);
+    unpack8(*reinterpret_cast<const uint4*>(src + i + half), hi);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const float2 t = cs[i + j];
+        a[j] = lo[j] * t.x - hi[j] * t.y;
+        b[j] = hi[j] * t.x + lo[j] * t.y;
+    }
+    *reinterpret_cast<uint4*>(dst + i) = pack8(a);
+    *reinterpret_cast<uint4*>(dst + i + half) = pack8(b);
+}
+
+__global__ void latent_prepare_vec_kernel(const __nv_bfloat16* __restrict__ down, int64_t ld_down, const __nv_bfloat16* __restrict__ q,
+                                          int64_t ld_q, const float* __restrict__ norm_w, const float2* __restrict__ table,
+                                          const int32_t* __restrict__ positions, const int32_t* __restrict__ seq_of_token,
+                                          const int32_t* __restrict__ page_table, int P, __nv_bfloat16* __restrict__ pool,
+                                          __nv_bfloat16* __restrict__ q_rot, int H, int Dn, int Dr, int R, int dims, int page_size,
+                                          float eps, int write_kv) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = dims / 2;
+    const float2* cs = table != nullptr ? table + (int64_t)pos * half : nullptr;
+    const int pairs = cs != nullptr ? half / 8 : 0;          // pieces that turn with a partner
+    const int plain = Dr / 8 - 2 * pairs;                    // pieces that pass
+    pdl_wait();
+    if (write_kv) {
+        const __nv_bfloat16* dr = down + (int64_t)t * ld_down;
+        float v[4][8];
+        float ss = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int c = (threadIdx.x + u * blockDim.x) * 8;
+            if (c < R) {
+                unpack8(*reinterpret_cast<const uint4*>(dr + c), v[u]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss += v[u][j] * v[u][j];
+            }
+        }
+        const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)R + eps);
+        const int page = page_table[(int64_t)seq_of_token[t] * P + pos / page_size];
+        __nv_bfloat16* row = pool + ((int64_t)page * page_size + pos % page_size) * (R + Dr);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int c = (threadIdx.x + u * blockDim.x) * 8;
+            if (c < R) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) v[u][j] = v[u][j] * inv * norm_w[c + j];
+                *reinterpret_cast<uint4*>(row + c) = pack8(v[u]);
+            }
+        }
+        for (int i = threadIdx.x; i < pairs + plain; i += blockDim.x) {
+            if (i < pairs) rotate_pieces(dr + R, row + R, cs, i * 8, half);
+            else *reinterpret_cast<uint4*>(row + R + dims + (i - pairs) * 8) = *reinterpret_cast<const uint4*>(dr + R + dims + (i - pairs) * 8);
+        }
+    }
+    const int per_head = pairs + plain;
+    for (int idx = threadIdx.x; idx < H * per_head; idx += blockDim.x) {
+        const int h = idx / per_head, i = idx - h * per_head;
+        const __nv_bfloat16* src = q + (int64_t)t * ld_q + (int64_t)h * (Dn + Dr) + Dn;
+        __nv_bfloat16* dst = q_rot + ((int64_t)t * H + h) * Dr;
+        if (i < pairs) rotate_pieces(src, dst, cs, i * 8, half);
+        else *reinterpret_cast<uint4*>(dst + dims + (i - pairs) * 8) = *reinterpret_cast<const uint4*>(src + dims + (i - pairs) * 8);
+    }
+}
+
 // One warp per (token, head). Scores with lanes over keys, weighted sums with lanes over channels.
 template <typename T>
 __global__ void latent_attention_generic_kernel(const T* __restrict__ q_lat, int64_t qs_t, int64_t qs_h,
@@ -279,6 +367,15 @@ XS_API int xs_latent_prepare(const void* down, int64_t ld_down, const void* q, i
     XS_REQUIRE(H > 0 && Dn > 0 && Dr > 0 && R > 0, "latent_prepare: %d heads of %d + %d, rank %d", H, Dn, Dr, R);
     XS_REQUIRE(dims >= 0 && dims % 2 == 0 && dims <= Dr, "latent_prepare: %d rotated channels of %d", dims, Dr);
     XS_REQUIRE(!write_kv || (pool != nullptr && page_table != nullptr && P > 0), "latent_prepare: no cache to write to");
+    const int turned = table != nullptr ? dims : 0;
+    if (dtype == XS_BF16 && R % 8 == 0 && R <= 4096 && Dr % 8 == 0 && Dn % 8 == 0 && turned % 16 == 0 && ld_down % 8 == 0 && ld_q % 8 == 0 &&
+        (uintptr_t)down % 16 == 0 && (uintptr_t)q % 16 == 0 && (uintptr_t)pool % 16 == 0 && (uintptr_t)q_rot % 16 == 0) {
+        xs_launch(latent_prepare_vec_kernel, dim3(T), dim3(128), 0, stream, (const __nv_bfloat16*)down, ld_down,
+                  (const __nv_bfloat16*)q, ld_q, norm_w, (const float2*)table, positions, seq_of_token, page_table, P,
+                  (__nv_bfloat16*)pool, (__nv_bfloat16*)q_rot, H, Dn, Dr, R, turned, page_size, eps, write_kv);
+        XS_LAUNCH_CHECK("latent_prepare");
+        return 0;
+    }
     XS_DISPATCH_DTYPE(dtype, TT,
                       xs_launch(latent_prepare_kernel<TT>, dim3(T), dim3(128), 0, stream, (const TT*)down, ld_down,
                                 (const TT*)q, ld_q, norm_w, (const float2*)table, positions, seq_of_token, page_table, P,
