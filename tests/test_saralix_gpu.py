@@ -139,6 +139,27 @@ def test_long_decoding(name, dtype, replayers, folders):
     check(name, dtype, tu.batch_trace(reqs, 2, prompt_frac=0.02), reqs, replayers, folders)
 
 
+def test_every_product_on_the_tcgen05_kernel(folders, monkeypatch):
+    """With the tcgen05 product forced for every number of rows, the clamped unit's activation runs in the gate/up
+    product's epilogue (D has widths in blocks of 8); whole prompts and single tokens against the oracle."""
+    from xpu_serve_b200.engine.model import load_model
+    from xpu_serve_b200.engine.replay import Replayer
+    from xpu_serve_b200.ops import lib as ops
+    monkeypatch.setenv("XS_MANY_ROWS_GEMM", "tcgen05")
+    rp = Replayer(load_model(folders("D", "bfloat16"), dtype="bfloat16"), 1024, None)
+    assert rp.model.rt.many_rows == "tcgen05"
+    seen = []
+    real = ops.gemm_tc_clamped
+    monkeypatch.setattr(ops, "gemm_tc_clamped", lambda *a, **k: (seen.append(a[0].shape[0]), real(*a, **k))[1])
+    reqs = requests_for("D", [70, 131, 9])
+    steps = tu.tail_trace(reqs, tail=6)
+    got = tu.collect(steps, tu.run_in_process(rp, steps), tiny.CONFIGS["D"]["vocab"])
+    ref = reference(folders("D", "bfloat16"), "D", reqs, "bfloat16")
+    gap, where, cos = tu.worst_gap(got, {k: v for k, v in ref.items() if k in got})
+    assert gap <= tiny.upper_limit("D", "bfloat16") and cos >= COS["bfloat16"], (gap, where, cos)
+    assert 125 in seen and 1 in seen           # a whole prompt's rows, and a single token's
+
+
 def test_a_lost_part_is_caught(replayers, folders, monkeypatch):
     """The bounds see a sink that is left out, a window one token too long, and a state that is not carried."""
     from xpu_serve_b200.ops import lib as ops

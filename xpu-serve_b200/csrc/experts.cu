@@ -20,32 +20,34 @@ __device__ __forceinline__ float sigmoid_f(float z) { return 1.0f / (1.0f + expf
 
 // ---------------------------------------------------------------------------------------------- clamped gated unit
 // out[t, f] = g * sigmoid(alpha g) * (u + shift), g = min(gate, limit), u = clamp(up, -limit, limit); a row of gu is
-// [F gate | F up].
+// [F gate | F up], or with interleave 8 blocks of 8 gate columns and the 8 up columns of the same outputs.
 template <typename T>
 __global__ void clamped_glu_kernel(const T* __restrict__ gu, T* __restrict__ out, int64_t total, int F, int64_t ld,
-                                   float limit, float alpha, float shift) {
+                                   float limit, float alpha, float shift, int interleave) {
     pdl_launch_dependents();
     pdl_wait();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = i / F;
         const int f = (int)(i - t * F);
-        const float g = fminf(to_f32(gu[t * ld + f]), limit);
-        const float u = fminf(fmaxf(to_f32(gu[t * ld + F + f]), -limit), limit);
+        const int64_t gi = interleave ? (int64_t)(f / interleave) * 2 * interleave + f % interleave : f;
+        const int64_t ui = interleave ? gi + interleave : (int64_t)F + f;
+        const float g = fminf(to_f32(gu[t * ld + gi]), limit);
+        const float u = fminf(fmaxf(to_f32(gu[t * ld + ui]), -limit), limit);
         out[i] = from_f32<T>(g * sigmoid_f(alpha * g) * (u + shift));
     }
 }
 
 // 8 outputs a thread, 16-byte loads and stores (bfloat16, F a multiple of 8, rows 16-byte aligned).
 __global__ void clamped_glu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int64_t total8,
-                                          int F8, int64_t ld, float limit, float alpha, float shift) {
+                                          int F8, int64_t ld, float limit, float alpha, float shift, int interleave) {
     pdl_launch_dependents();
     pdl_wait();
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (int64_t)gridDim.x * blockDim.x) {
         const int64_t t = i / F8;
         const int j = (int)(i - t * F8);
         const __nv_bfloat16* row = gu + t * ld;
-        const uint4 g = *reinterpret_cast<const uint4*>(row + 8 * j);
-        const uint4 u = *reinterpret_cast<const uint4*>(row + 8 * (int64_t)F8 + 8 * j);
+        const uint4 g = *reinterpret_cast<const uint4*>(row + (interleave ? 16 * j : 8 * j));
+        const uint4 u = *reinterpret_cast<const uint4*>(row + (interleave ? 16 * j + 8 : 8 * (int64_t)F8 + 8 * j));
         const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
         const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
         uint4 o;
@@ -363,14 +365,15 @@ __global__ void moe_combine_kernel(const TI* __restrict__ rows_out, const int32_
 }  // namespace
 
 XS_API int xs_clamped_glu(const void* gu, void* out, int dtype, int T, int F, int64_t ld, float limit, float alpha,
-                          float shift, cudaStream_t stream) {
+                          float shift, int interleave, cudaStream_t stream) {
     if (T == 0) return 0;
     XS_REQUIRE(T > 0 && F > 0 && ld >= 2 * (int64_t)F, "clamped_glu: %d rows, %d columns, stride %lld", T, F, (long long)ld);
+    XS_REQUIRE(interleave == 0 || (interleave == 8 && F % 8 == 0), "clamped_glu: interleave %d with %d columns", interleave, F);
     if (dtype == XS_BF16 && F % 8 == 0 && ld % 8 == 0 && (uintptr_t)gu % 16 == 0 && (uintptr_t)out % 16 == 0) {
         const int64_t total8 = (int64_t)T * (F / 8);
         const int blocks8 = (int)((total8 + 255) / 256 < 148 * 32 ? (total8 + 255) / 256 : 148 * 32);
         xs_launch(clamped_glu_bf16x8_kernel, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out,
-                  total8, F / 8, ld, limit, alpha, shift);
+                  total8, F / 8, ld, limit, alpha, shift, interleave);
         XS_LAUNCH_CHECK("clamped_glu");
         return 0;
     }
@@ -378,7 +381,7 @@ XS_API int xs_clamped_glu(const void* gu, void* out, int dtype, int T, int F, in
     const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     XS_DISPATCH_DTYPE(dtype, TT,
                       xs_launch(clamped_glu_kernel<TT>, dim3(blocks), dim3(256), 0, stream, (const TT*)gu, (TT*)out, total,
-                                F, ld, limit, alpha, shift));
+                                F, ld, limit, alpha, shift, interleave));
     XS_LAUNCH_CHECK("clamped_glu");
     return 0;
 }

@@ -47,7 +47,19 @@ struct GemmTcParams {
     int T, N, K, ksplit, epilogue, out_f32;
     int vec;                  // rows of out start on 16-byte boundaries: the many-token epilogue may store vectors
     int64_t ldo;
+    // the gated epilogue's activation: limit 0: silu(gate) * up; limit > 0: g = min(gate, limit), u = clamp(up, -limit, limit),
+    // g * sigmoid(alpha g) * (u + shift)
+    float glu_limit, glu_alpha, glu_shift;
 };
+
+__device__ __forceinline__ float gated_unit(const GemmTcParams& p, float g, float u) {
+    if (p.glu_limit > 0.0f) {
+        g = fminf(g, p.glu_limit);
+        u = fminf(fmaxf(u, -p.glu_limit), p.glu_limit);
+        return g / (1.0f + __expf(-p.glu_alpha * g)) * (u + p.glu_shift);
+    }
+    return g / (1.0f + __expf(-g)) * u;
+}
 
 // Instruction descriptor of this file's single-CTA products: M = 128, N = n.
 __host__ __device__ constexpr uint32_t instr_desc(int n) { return instr_desc_mn(BM, n); }
@@ -66,7 +78,7 @@ __device__ __forceinline__ void emit(const GemmTcParams& p, float v, int row, in
     if (p.epilogue == EPI_SWIGLU) {
         const float up = __shfl_xor_sync(0xffffffffu, v, 8);
         if ((lane & 8) == 0 && row + 8 < p.N && token < p.T) {
-            const float a = v / (1.0f + __expf(-v)) * up;
+            const float a = gated_unit(p, v, up);
             const int64_t at = (int64_t)token * p.ldo + (row >> 4) * 8 + (row & 7);
             if (p.out_f32) ((float*)p.out)[at] = a; else ((__nv_bfloat16*)p.out)[at] = __float2bfloat16_rn(a);
         }
@@ -96,7 +108,7 @@ __device__ __forceinline__ void emit16(const GemmTcParams& p, const uint32_t* r,
     if (p.epilogue == EPI_SWIGLU) {   // rows f0..f0+7 are gates, f0+8..f0+15 their up rows; N is a multiple of 16
         float a[8];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) a[j] = v[j] / (1.0f + __expf(-v[j])) * v[j + 8];
+        for (int j = 0; j < 8; ++j) a[j] = gated_unit(p, v[j], v[j + 8]);
         const int64_t at = (int64_t)token * p.ldo + (f0 >> 1);
         if (p.out_f32) {
             float* o = (float*)p.out + at;
@@ -864,9 +876,9 @@ XS_API int64_t xs_gemm_tc_scratch_bytes(int T, int N, int ksplit) {
 // epilogue: 0 store (out_dtype), 1 residual (out is float32 [T, N], += result), 2 SwiGLU (out is [T, N / 2]).
 // ksplit > 1: scratch of xs_gemm_tc_scratch_bytes; its last 64 KiB are counters that are zero between calls.
 // status: one device int that the kernel sets non-zero if a wait inside it gave up (the result is then invalid).
-XS_API int xs_gemm_tc(const void* x, const void* w, const float* bias, void* out, int out_dtype, int epilogue, int T, int N,
-                      int K, int64_t ldx, int64_t ldw, int64_t ldo, int ksplit, void* scratch, int64_t scratch_bytes,
-                      int* status, cudaStream_t stream) {
+static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* out, int out_dtype, int epilogue, int T, int N,
+                        int K, int64_t ldx, int64_t ldw, int64_t ldo, int ksplit, void* scratch, int64_t scratch_bytes,
+                        int* status, float glu_limit, float glu_alpha, float glu_shift, cudaStream_t stream) {
     if (T == 0 || N == 0) return 0;
     XS_REQUIRE(xs_gemm_tc_supports(T, N, K, ldx, ldw), "gemm (tcgen05): T %d, N %d, K %d, strides %lld, %lld not supported", T,
                N, K, (long long)ldx, (long long)ldw);
@@ -885,6 +897,7 @@ XS_API int xs_gemm_tc(const void* x, const void* w, const float* bias, void* out
     p.T = T; p.N = N; p.K = K; p.ksplit = ksplit; p.epilogue = epilogue; p.out_f32 = out_dtype == XS_F32;
     p.ldo = ldo;
     p.vec = 0;
+    p.glu_limit = glu_limit; p.glu_alpha = glu_alpha; p.glu_shift = glu_shift;
     if (ksplit > 1) {
         const int64_t need = xs_gemm_tc_scratch_bytes(T, N, ksplit);
         const int64_t tiles = (int64_t)ceil_div_i(N, BM) * ceil_div_i(T, bn);
@@ -931,6 +944,22 @@ XS_API int xs_gemm_tc(const void* x, const void* w, const float* bias, void* out
 }
 
 
+XS_API int xs_gemm_tc(const void* x, const void* w, const float* bias, void* out, int out_dtype, int epilogue, int T, int N,
+                      int K, int64_t ldx, int64_t ldw, int64_t ldo, int ksplit, void* scratch, int64_t scratch_bytes,
+                      int* status, cudaStream_t stream) {
+    return gemm_tc_impl(x, w, bias, out, out_dtype, epilogue, T, N, K, ldx, ldw, ldo, ksplit, scratch, scratch_bytes, status, 0.0f,
+                        1.0f, 0.0f, stream);
+}
+
+// The gated epilogue (2) with the clamped activation: g = min(gate, limit), u = clamp(up, -limit, limit),
+// out = g * sigmoid(alpha g) * (u + shift).
+XS_API int xs_gemm_tc_clamped(const void* x, const void* w, void* out, int out_dtype, int T, int N, int K, int64_t ldx, int64_t ldw,
+                              int64_t ldo, float limit, float alpha, float shift, int* status, cudaStream_t stream) {
+    XS_REQUIRE(limit > 0.0f, "gemm (tcgen05): the clamped unit's limit must be positive");
+    return gemm_tc_impl(x, w, nullptr, out, out_dtype, EPI_SWIGLU, T, N, K, ldx, ldw, ldo, 1, nullptr, 0, status, limit, alpha, shift,
+                        stream);
+}
+
 // out[r] = W[expert of r's tile] . x[r] for the row tiles of a plan on the device (csrc/experts.cu: xs_moe_plan with
 // padding, tiles of 128 rows). x: [rows_cap, K] with every expert's rows padded to whole tiles; w: [E * N, K], the
 // experts' weights one under another; out: [rows_cap, N] (N / 2 with the SwiGLU epilogue, whose weight is stacked in
@@ -955,6 +984,7 @@ XS_API int xs_gemm_tc_grouped(const void* x, const void* w, void* out, int out_d
     p.status = status;
     p.T = rows_cap; p.N = N; p.K = K; p.ksplit = 1; p.epilogue = epilogue; p.out_f32 = out_dtype == XS_F32;
     p.ldo = ldo;
+    p.glu_limit = 0.0f; p.glu_alpha = 1.0f; p.glu_shift = 0.0f;
     const int esz = p.out_f32 ? 4 : 2;
     p.vec = ((uintptr_t)out % 16 == 0) && ((ldo * esz) % 16 == 0);
     alignas(64) CUtensorMap mw, mx;

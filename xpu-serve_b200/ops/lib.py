@@ -55,7 +55,8 @@ def _signatures(lib) -> None:
         "xs_note_tokens": [P, P, I, I, P, P, I, P],
         "xs_add_layernorm": [P, P, I, P, P, P, I, P, I, I, F, F, P],
         "xs_grouped_rmsnorm": [P, P, P, I, I, I, I, F, P],
-        "xs_clamped_glu": [P, P, I, I, I, L, F, F, F, P],
+        "xs_clamped_glu": [P, P, I, I, I, L, F, F, F, I, P],
+        "xs_gemm_tc_clamped": [P, P, P, I, I, I, I, L, L, L, F, F, F, P, P],
         "xs_moe_route": [P, I, I, I, P, P, P],
         "xs_moe_logits": [P, L, P, P, I, I, I, I, P],
         "xs_moe_plan": [P, I, I, I, I, P, P, P, P],
@@ -798,9 +799,9 @@ def grouped_rmsnorm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, groups: i
                                      int(groups), float(eps), _stream()))
 
 
-def clamped_glu(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, shift: float) -> None:
+def clamped_glu(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, shift: float, interleave: int = 0) -> None:
     """out = g * sigmoid(alpha g) * (u + shift), g = min(gate, limit), u = clamp(up, -limit, limit); a row of gu is
-    [gate | up]."""
+    [gate | up], or with interleave 8 blocks of 8 gate and 8 up columns."""
     _need(out, "out", gu.dtype)
     if not gu.is_cuda or gu.dim() != 2 or gu.stride(1) != 1:
         raise KernelError("gate_up must be a CUDA matrix with contiguous rows")
@@ -808,7 +809,23 @@ def clamped_glu(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float,
     if gu.shape[0] != T or gu.shape[1] < 2 * F:
         raise KernelError(f"gate_up is {tuple(gu.shape)} for an output of {tuple(out.shape)}")
     _check(load().xs_clamped_glu(gu.data_ptr(), out.data_ptr(), _code(gu), T, F, gu.stride(0), float(limit), float(alpha),
-                                 float(shift), _stream()))
+                                 float(shift), int(interleave), _stream()))
+
+
+def gemm_tc_clamped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, shift: float) -> None:
+    """The tcgen05 product with the clamped gated unit in its epilogue: w [2 F, K] stacked in blocks of 8 gate and 8 up
+    rows, out[T, F] = g * sigmoid(alpha g) * (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
+    for t, name in ((x, "x"), (w, "w")):
+        if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.dtype != torch.bfloat16:
+            raise KernelError(f"gemm (tcgen05): {name} must be a bfloat16 CUDA matrix with contiguous rows")
+    T, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or tuple(out.shape) != (T, N // 2) or out.stride(1) != 1:
+        raise KernelError(f"gemm (tcgen05): x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    mark_bounded(x.device)
+    _check(load().xs_gemm_tc_clamped(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), T, N, K, x.stride(0), w.stride(0),
+                                     out.stride(0), float(limit), float(alpha), float(shift), gemm_tc_status(x.device).data_ptr(),
+                                     _stream()))
 
 
 # ------------------------------------------------------------------------------- routed experts

@@ -32,14 +32,26 @@ class ClampedGLU(FeedForward):
     def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
         self.spec, self.rt = spec, rt
         n = spec.names
-        self.w_gate_up = rt.matrix(torch.cat([weights[n["gate"]].to(torch.float32), weights[n["up"]].to(torch.float32)], 0))
+        gate, up = weights[n["gate"]].to(torch.float32), weights[n["up"]].to(torch.float32)
+        F, H = spec.intermediate, spec.hidden
+        # bfloat16 and widths in blocks of 8: gate and up rows stacked in blocks of 8 and 8, as SwiGLU stacks them, so that
+        # the tcgen05 product of long prompts applies the activation in its epilogue
+        self.interleave = 8 if (rt.mode == "bfloat16" and F % 8 == 0) else 0
+        if self.interleave:
+            stacked = torch.stack([gate.view(F // 8, 8, H), up.view(F // 8, 8, H)], 1).reshape(2 * F, H)
+        else:
+            stacked = torch.cat([gate, up], 0)
+        self.w_gate_up = rt.matrix(stacked)
         self.w_down = rt.matrix(weights[n["down"]])
 
     def forward(self, y, step) -> torch.Tensor:
         rt, s = self.rt, self.spec
-        gu = rt.linear(y, self.w_gate_up, "ffn_gate_up")
         act = rt.ws.get("ffn_act", (y.shape[0], s.intermediate), rt.act_dtype)
-        ops.clamped_glu(gu, act, s.limit, s.alpha, s.up_shift)
+        if self.interleave and rt.tensor_core_product(y, self.w_gate_up, fused=True):
+            ops.gemm_tc_clamped(y, self.w_gate_up, act, s.limit, s.alpha, s.up_shift)
+        else:
+            gu = rt.linear(y, self.w_gate_up, "ffn_gate_up")
+            ops.clamped_glu(gu, act, s.limit, s.alpha, s.up_shift, self.interleave)
         return rt.linear(act, self.w_down, "ffn_out")
 
 
