@@ -139,6 +139,24 @@ def test_long_decoding(name, dtype, replayers, folders):
     check(name, dtype, tu.batch_trace(reqs, 2, prompt_frac=0.02), reqs, replayers, folders)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["M", "N", "D"])
+def test_long_prompts_run_the_recurrence_in_chunks(name, dtype, replayers, folders):
+    """Prompts of 300 and 520 tokens beside one of 40 in one step: the Mamba-2 layers cut them into chunks of 128 that run side
+    by side (three and five, the last ones partly filled), each sequence's state carried from chunk to chunk and on into the
+    single tokens that follow; the attention layers see keys four and eight pages back."""
+    from xpu_serve_b200.ops import lib as ops
+    reqs = {"a": tiny.prompt(name, 306, salt=5), "b": tiny.prompt(name, 526, salt=6), "c": tiny.prompt(name, 46, salt=7)}
+    seen = []
+    real = ops.mamba2_scan
+    ops.mamba2_scan = lambda *a, **k: (seen.append(a[-1] if a[-1] is not None and not isinstance(a[-1], int) else k.get("chunks")), real(*a, **k))[1]
+    try:
+        check(name, dtype, tu.batch_trace(reqs, 3, prompt_frac=0.985), reqs, replayers, folders, max_tokens=1280)
+    finally:
+        ops.mamba2_scan = real
+    assert any(c is not None and c[0].shape[0] == 3 + 5 + 1 for c in seen), "the long prompts did not take the chunked scan"
+
+
 def test_every_product_on_the_tcgen05_kernel(folders, monkeypatch):
     """With the tcgen05 product forced for every number of rows, the clamped unit's activation runs in the gate/up
     product's epilogue (D has widths in blocks of 8); whole prompts and single tokens against the oracle."""
