@@ -303,72 +303,71 @@ def plain_greedy(cfg, W, prompt, n):
     return out, margins
 
 
+@pytest.mark.parametrize("precision,name", [("f32", "M"), ("bf16", "D")])
 @pytest.mark.parametrize("chunk", [None, 16])
-def test_greedy_generation_through_the_engine(folders, chunk):
+def test_greedy_generation_through_the_engine(folders, chunk, precision, name):
     """The framework's own entry point and scheduler: three unequal prompts as one batch (with `chunk`, prompts in
-    pieces of 16 tokens), greedy, against the plain implementation run token by token."""
+    pieces of 16 tokens), greedy, against the plain implementation run token by token. In float32 every token must be the
+    oracle's; in bfloat16 a sequence is followed until the oracle's own choice is a near tie (or, with experts, a router's
+    close call lies behind it)."""
     from xpu_serve_b200 import GenerateRequest, SamplingParams
     from xpu_serve_b200.engine.engine import Engine
-    folder = folders("M", "float32")
+    dtype = {"f32": "float32", "bf16": "bfloat16"}[precision]
+    folder = folders(name, dtype)
     cfg, W = load_folder(folder)
     kw = {} if chunk is None else {"prefill_chunk": chunk}
-    engine = Engine(folder, precision="f32", ctx=256, max_batch=8, **kw)
-    prompts = [tiny.prompt("M", n, salt=i) for i, n in enumerate((3, 41, 18))]
+    engine = Engine(folder, precision=precision, ctx=256, max_batch=8, **kw)
+    prompts = [tiny.prompt(name, n, salt=i) for i, n in enumerate((3, 41, 18))]
     res = engine.generate([GenerateRequest(p, SamplingParams(temperature=0.0), 9, []) for p in prompts])
+    followed = 0
     for p, r in zip(prompts, res):
-        want, margins = plain_greedy(cfg, W, p, 9)
-        assert min(margins) > 1e-4, "the test's own tokens are near ties; pick another prompt"
-        assert r.finish == "length" and r.tokens == want
+        assert r.finish == "length" and len(r.tokens) == 9
+        if precision == "f32":
+            want, margins = plain_greedy(cfg, W, p, 9)
+            assert min(margins) > 1e-4, "the test's own tokens are near ties; pick another prompt"
+            assert r.tokens == want
+            continue
+        seq = list(p)
+        for t in r.tokens:
+            close = np.full(len(seq), np.inf)
+            logits = plain.forward(cfg, W, seq, margins=close)[-1]
+            order = np.argsort(-logits)
+            if (logits[order[0]] - logits[order[1]]) / np.abs(logits).max() < 0.03 or close.min() < CLOSE_CALL["bfloat16"]:
+                break
+            assert t == int(order[0]), (len(seq) - len(p), t, int(order[0]))
+            followed += 1
+            seq.append(t)
+    assert precision == "f32" or followed >= 3, "near ties everywhere; pick other prompts"
     engine.stepper.cache.check()
     assert engine.stepper.cache.slots.held_count == 0
 
 
-@pytest.mark.parametrize("tokens,experts,top,width,ff", [(9, 5, 2, 64, 24), (300, 6, 3, 72, 40), (130, 3, 1, 256, 136)])
-def test_routed_products_on_tensor_cores(tokens, experts, top, width, ff):
-    """The plan with padded tiles, the gather, both grouped tcgen05 products and the combine, against float64: some
-    experts with no row, some with more than one tile, widths that are no multiple of the tiles."""
-    from xpu_serve_b200.ops import lib as ops
-    g = torch.Generator().manual_seed(tokens)
-    x = (torch.randn(tokens, width, generator=g) * 0.5).bfloat16()
-    w_gate = (torch.randn(experts, ff, width, generator=g) * 0.2).bfloat16()
-    w_up = (torch.randn(experts, ff, width, generator=g) * 0.2).bfloat16()
-    w_down = (torch.randn(experts, width, ff, generator=g) * 0.2).bfloat16()
-    logits = torch.randn(tokens, experts, generator=g)
-    logits[:, 1] -= 50.0                                    # an expert that nobody chooses
-    logits[::3, 2] = logits[::3, 0]                         # equal logits: the lower index goes first
-    n = tokens * top
-    dev = "cuda"
-    ids = torch.empty(n, dtype=torch.int32, device=dev)
-    wts = torch.empty(n, dtype=torch.float32, device=dev)
-    place = torch.empty(n, dtype=torch.int32, device=dev)
-    tiles = ops.moe_max_tiles_of(n, experts, 128)
-    source = torch.empty(128 * tiles, dtype=torch.int32, device=dev)
-    meta = torch.empty(4 + 3 * tiles, dtype=torch.int32, device=dev)
-    ops.moe_route(logits.to(dev), top, ids, wts)
-    ops.moe_plan(ids, experts, place, source, meta, tile_rows=128)
-    rows_in = torch.empty(128 * tiles, width, dtype=torch.bfloat16, device=dev)
-    ops.moe_gather(x.to(dev), source, top, rows_in)
-    stacked = torch.stack([torch.stack([w_gate[e].view(ff // 8, 8, width), w_up[e].view(ff // 8, 8, width)], 1).reshape(2 * ff, width)
-                           for e in range(experts)]).to(dev)
-    act = torch.empty(128 * tiles, ff, dtype=torch.bfloat16, device=dev)
-    ops.gemm_tc_grouped(rows_in, stacked, act, meta, tiles, glu=True)
-    rows_out = torch.empty(128 * tiles, width, dtype=torch.bfloat16, device=dev)
-    ops.gemm_tc_grouped(act, w_down.to(dev), rows_out, meta, tiles, glu=False)
-    y = torch.empty(tokens, width, dtype=torch.bfloat16, device=dev)
-    ops.moe_combine(rows_out, place, wts, y, top)
-    torch.cuda.synchronize()
-    assert int(ops.gemm_tc_status(torch.device(dev)).item()) == 0
-    # float64, with the device's own choices checked against a plain top-k
-    order = torch.argsort(-logits, dim=1, stable=True)[:, :top]
-    assert torch.equal(ids.cpu().view(tokens, top).long(), order)
-    chosen = torch.gather(logits.double(), 1, order)
-    weight = torch.softmax(chosen, dim=1)
-    ref = torch.zeros(tokens, width, dtype=torch.float64)
-    xd = x.double()
-    for t in range(tokens):
-        for k in range(top):
-            e = int(order[t, k])
-            gt, up = w_gate[e].double() @ xd[t], w_up[e].double() @ xd[t]
-            ref[t] += weight[t, k] * (w_down[e].double() @ (gt / (1 + torch.exp(-gt)) * up))
-    gap = (y.double().cpu() - ref).abs().max() / ref.abs().max()
-    assert gap < 2e-2, gap
+@pytest.mark.parametrize("chunk", [None, 16])
+def test_generation_with_experts_in_bfloat16_follows_replay(folders, replayers, chunk):
+    """With experts the oracle's choice of experts is a close call too often at 16 bits to follow it for long, so here the
+    engine (prompts as captured graphs of a fixed number of rows, or in pieces of 16 tokens; decode graphs, one step ahead of
+    the loop) is held against trace replay of the same tokens (prompts as plain launches): two paths through the same
+    kernels. A token may differ only where replay's own two best logits are within a hundredth of the largest."""
+    from xpu_serve_b200 import GenerateRequest, SamplingParams
+    from xpu_serve_b200.engine.engine import Engine
+    folder = folders("N", "bfloat16")
+    kw = {} if chunk is None else {"prefill_chunk": chunk}
+    engine = Engine(folder, precision="bf16", ctx=256, max_batch=8, **kw)
+    prompts = [tiny.prompt("N", n, salt=i) for i, n in enumerate((3, 41, 18))]
+    res = engine.generate([GenerateRequest(p, SamplingParams(temperature=0.0), 9, []) for p in prompts])
+    rp = replayers("N", "bfloat16")
+    same = 0
+    for p, r in zip(prompts, res):
+        assert r.finish == "length" and len(r.tokens) == 9
+        logits = rp.run_step({"step": 0, "entries": [{"id": "g", "tokens": p, "want": [0, len(p) - 1]}], "end": []})[-1]
+        for i, t in enumerate(r.tokens):
+            order = np.argsort(-logits)
+            if t != int(order[0]):
+                assert (logits[order[0]] - logits[order[1]]) / np.abs(logits).max() < 1e-2, (i, t, int(order[0]))
+                break
+            same += 1
+            logits = rp.run_step({"step": i + 1, "entries": [{"id": "g", "tokens": [t], "want": [0]}], "end": []})[0]
+        rp.run_step({"step": 99, "entries": [], "end": ["g"]})
+    assert same >= 20
+    engine.stepper.cache.check()
+    assert engine.stepper.cache.slots.held_count == 0 and rp.cache.slots.held_count == 0
