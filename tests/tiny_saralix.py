@@ -63,7 +63,8 @@ CONFIGS = {
         ("mamba2", mamba(8, 8, 8, 1, 3, 8), dense(72, 4.0)),
     ]),
     # one mechanism each (the feed-forward ones behind the smallest mixer)
-    "gated": model(40, 150, [("latent_attention", latent(2, 14, 6, 10, 28, 0.25, base=900.0, scaling=STRETCH), None)]),
+    # (only the first 4 of the 6 rotated channels turn: the rotation's own width may be smaller than the part it stands in)
+    "gated": model(40, 150, [("latent_attention", latent(2, 14, 6, 10, 28, 0.25, base=900.0, dims=4, scaling=STRETCH), None)]),
     "windowed": model(40, 150, [("latent_attention_2", latent(3, 8, 10, 12, 20, 0.3, base=50.0, window=9), None)]),
     "recurrent": model(40, 150, [("mamba2", mamba(4, 10, 24, 2, 4, 2), None)]),
     "dense": model(40, 150, [("mamba2", mamba(1, 8, 4, 1, 2, 1), dense(90, 1.0))]),
