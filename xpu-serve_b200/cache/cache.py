@@ -106,7 +106,7 @@ class StateGroup:
     def __init__(self, need: StateNeed, calls: List[Tuple[int, int]], max_slots: int, compute_dtype: torch.dtype, device):
         self.need = need
         self.calls = list(calls)
-        dtype = torch.float32 if need.dtype == "float32" else compute_dtype
+        dtype = {"float32": torch.float32, "int32": torch.int32}.get(need.dtype, compute_dtype)
         # One row more than there are slots: the state of padding rows. The calls' tensors are pieces of one
         # allocation, each from a 256-byte boundary on, so that a batch's slots are zeroed with one launch for the
         # whole group instead of one a call.

@@ -55,6 +55,10 @@ class AttentionSpec:
         "q_bias": "self_attn.q_proj.bias", "k_bias": "self_attn.k_proj.bias", "v_bias": "self_attn.v_proj.bias"})
     kind: str = "attention"
     qkv_bias: bool = False   # q, k and v projections with a bias each (LFM3 has none)
+    v_dim: int = 0           # size of a value head when it differs from head_dim (0: head_dim); needs position None
+    chunk: int = 0           # C > 0: a query at pos sees the earlier keys of its own block only, j >= pos - pos % C
+                             # (blocks of C positions counted from the sequence's position 0); excludes `window`
+    own_kv: bool = True      # False: the layer has no k, v and k-norm tensors; its call reads another call's cache
 
 
 @dataclass(frozen=True)
@@ -161,6 +165,33 @@ class Mamba2Spec:
 
 
 @dataclass(frozen=True)
+class MLstmSpec:
+    """The matrix-memory recurrence of xLSTM (mLSTM) per head: a state [dim, vdim], a normaliser [dim] and a running
+    maximum, float32, with log-space input and forget gates whose pre-activations are soft-capped at +-gate_cap
+    (parts/mlstm.py has the formulas). The heads' outputs are divided by their root mean square (`eps`), multiplied by
+    a weight over all heads and by sigmoid of an output gate, then projected."""
+    hidden: int
+    heads: int
+    dim: int
+    vdim: int
+    gate_cap: float
+    eps: float
+    names: Dict[str, str] = field(default_factory=lambda: {
+        "q": "mix.q", "k": "mix.k", "v": "mix.v", "gate": "mix.g", "o": "mix.o", "norm": "mix.norm",
+        "i": "mix.i", "i_bias": "mix.i.b", "f": "mix.f", "f_bias": "mix.f.b"})
+    kind: str = "mlstm"
+
+
+@dataclass(frozen=True)
+class SquaredReluSpec:
+    """down(max(up x, 0)^2)."""
+    hidden: int
+    intermediate: int
+    names: Dict[str, str] = field(default_factory=lambda: {"up": "mlp.up", "down": "mlp.down"})
+    kind: str = "squared_relu"
+
+
+@dataclass(frozen=True)
 class ClampedGLUSpec:
     """down(g * sigmoid(alpha g) * (u + up_shift)) with g = min(gate x, limit), u = clamp(up x, -limit, limit)."""
     hidden: int
@@ -174,14 +205,23 @@ class ClampedGLUSpec:
 
 @dataclass(frozen=True)
 class RoutedExpertsSpec:
-    """`experts` SwiGLU feed-forwards without biases, of which a token uses the `top` with the largest router
-    logits (float32), weighted by the softmax over those logits alone."""
+    """`experts` gated feed-forwards without biases, of which a token uses the `top` with the largest router
+    logits (float32), weighted by the softmax over those logits alone (which equals the softmax over all logits
+    divided by the chosen ones' sum) times `route_scale`. `limit` 0: the experts are SwiGLU units; > 0: clamped gated
+    units with that limit, `alpha` and `up_shift` (ClampedGLUSpec). `shared`: a clamped gated unit that every token
+    uses, added to the sum times sigmoid(x . w) of the one-row matrix names["shared_gate"]."""
     hidden: int
     intermediate: int
     experts: int
     top: int
+    route_scale: float = 1.0
+    limit: float = 0.0
+    alpha: float = 1.702
+    up_shift: float = 1.0
+    shared: Optional["ClampedGLUSpec"] = None
     names: Dict[str, str] = field(default_factory=lambda: {
-        "router": "mlp.router", "gate": "mlp.e{e}.gate", "up": "mlp.e{e}.up", "down": "mlp.e{e}.down"})
+        "router": "mlp.router", "gate": "mlp.e{e}.gate", "up": "mlp.e{e}.up", "down": "mlp.e{e}.down",
+        "shared_gate": "mlp.shared.sg"})
     kind: str = "routed_experts"
 
 
@@ -192,6 +232,23 @@ class NormSpec:
     width: int
     eps: float
     kind: str = "rmsnorm"    # "layernorm": (x - mean) * (variance + eps)^(-1/2) * w, no bias (parts/layernorm.py)
+
+
+@dataclass(frozen=True)
+class PairHashEmbeddingSpec:
+    """Token embedding = table[tok] * scale + pair[(prev * mul_prev + tok * mul_cur) mod buckets] (row `buckets` for a
+    sequence's first token) + a sine/cosine vector of the position (entries 2i and 2i + 1: sin and cos of
+    pos * theta^(-2i / width)), then an RMS norm. A sequence's last token is part of its state."""
+    width: int
+    vocab: int
+    scale: float
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    eps: float
+    theta: float = 10000.0
+    names: Dict[str, str] = field(default_factory=lambda: {"table": "embed", "pair": "bigram", "norm": "embed.norm"})
+    kind: str = "pair_hash"
 
 
 @dataclass(frozen=True)
@@ -207,7 +264,8 @@ class LayerSpec:
     names: Dict[str, str] = field(default_factory=lambda: {
         "pre_mixer": "operator_norm.weight", "post_mixer": "post_operator_norm.weight",
         "pre_ffn": "ffn_norm.weight", "post_ffn": "post_ffn_norm.weight"})
-    kind: str = "pre_norm"   # the arrangement (registry.register_arrangement); the formula above is "pre_norm"
+    kind: str = "pre_norm"   # the arrangement (registry.register_arrangement); the formula above is "pre_norm";
+                             # "branch_norm": h += post(mixer(h)); h += post(ffn(h)), no norm before a sublayer
 
 
 @dataclass(frozen=True)
@@ -235,6 +293,7 @@ class ModelSpec:
     logit_cap: float = 0.0    # > 0: logits = cap * tanh(logits / cap) (0: none, LFM3's)
     prefixes: Tuple[str, ...] = ("model.",)   # tried in turn for "<prefix>embed_tokens.weight"
     ignorable: Tuple[str, ...] = ()           # regular expressions: tensors of a folder that match are neither needed nor refused
+    embedding: Optional[object] = None        # a spec with a `kind` (registry.register_embedding); None: table[tok] * embed_scale
     names: Dict[str, str] = field(default_factory=lambda: {
         "embed": "embed_tokens.weight", "final_norm": "embedding_norm.weight",
         "head": "lm_head.weight"})   # "head" is looked up without the model prefix

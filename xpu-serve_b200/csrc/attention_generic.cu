@@ -216,7 +216,7 @@ __global__ void attention_generic_kernel(const T* __restrict__ q, const T* __res
     for (int d = lane; d < D; d += 32) qs[d] = to_f32(qrow[d]) * scale;
     __syncwarp();
 
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int lo = xs_first_visible(pos, window);
     float m = -INFINITY, l = 0.0f;
     float acc[kMaxHeadDim / 32];
 #pragma unroll
@@ -314,7 +314,7 @@ XS_API int xs_attention_generic(const void* q, const void* pool, const int32_t* 
     if (T == 0) return 0;
     XS_REQUIRE(D > 0 && D % 2 == 0 && D <= kMaxHeadDim, "attention: head size %d (even, at most %d)", D, kMaxHeadDim);
     XS_REQUIRE(Hq > 0 && Hkv > 0 && Hq % Hkv == 0, "attention: %d heads over %d kv heads", Hq, Hkv);
-    XS_REQUIRE(window >= 0 && page_size > 0 && P > 0, "attention: window %d, page size %d, %d pages", window, page_size, P);
+    XS_REQUIRE(page_size > 0 && P > 0, "attention: window %d, page size %d, %d pages", window, page_size, P);
     const int warps = 4;
     const int blocks = ceil_div_i((int64_t)T * Hq, warps);
     const size_t smem = (size_t)warps * D * sizeof(float);

@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(NTHREADS, (D <= 64 ? 4 : 2)) attention_mma_ker
     const int kv_len = p.kv_lens[seq];
     const int pos0 = kv_len - q_len + t0;
     const int hi = pos0 + nt;                                     // keys [lo, hi) matter to this tile
-    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int lo = xs_first_visible(pos0, p.window);
     const int b_lo = lo / BN, nb = (hi + BN - 1) / BN - b_lo;
     const int bs = b_lo + (int)((int64_t)nb * split / p.splits);
     const int be = b_lo + (int)((int64_t)nb * (split + 1) / p.splits);
@@ -190,7 +190,7 @@ __global__ void __launch_bounds__(NTHREADS, (D <= 64 ? 4 : 2)) attention_mma_ker
             // scale, mask, running max. A block that every row of the tile sees whole (all of it at or before
             // the tile's first position and inside every row's window) needs no per-element test.
             const int key0 = b * BN + (lane & 3) * 2;
-            const bool whole = b * BN + BN - 1 <= pos0 && (p.window == 0 || pos0 + nt - 1 - b * BN < p.window);
+            const bool whole = b * BN + BN - 1 <= pos0 && b * BN >= xs_first_visible(pos0 + nt - 1, p.window);
             float mx1 = -INFINITY, mx2 = -INFINITY;
             if (whole) {
 #pragma unroll
@@ -209,8 +209,8 @@ __global__ void __launch_bounds__(NTHREADS, (D <= 64 ? 4 : 2)) attention_mma_ker
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int key = key0 + i * 8 + e;
-                        const bool v1 = key <= pos1 && (p.window == 0 || pos1 - key < p.window);
-                        const bool v2 = key <= pos2 && (p.window == 0 || pos2 - key < p.window);
+                        const bool v1 = xs_visible(pos1, key, p.window);
+                        const bool v2 = xs_visible(pos2, key, p.window);
                         s[i][e] = v1 ? s[i][e] * p.scale_log2 : -INFINITY;
                         s[i][2 + e] = v2 ? s[i][2 + e] * p.scale_log2 : -INFINITY;
                         mx1 = fmaxf(mx1, s[i][e]);
@@ -330,7 +330,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_decode_mma_kernel(const At
     const int kv_len = p.kv_lens[seq];
     const int pos0 = kv_len - q_len + t0;
     const int hi = pos0 + nt;
-    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int lo = xs_first_visible(pos0, p.window);
     const int b_lo = lo / BN, nb = (hi + BN - 1) / BN - b_lo;
     const int bs = b_lo + (int)((int64_t)nb * split / p.splits);
     const int be = b_lo + (int)((int64_t)nb * (split + 1) / p.splits);
@@ -437,8 +437,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_decode_mma_kernel(const At
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int key = key0 + i * 8 + e;
-                const bool v1 = key <= pos1 && (p.window == 0 || pos1 - key < p.window);
-                const bool v2 = key <= pos2 && (p.window == 0 || pos2 - key < p.window);
+                const bool v1 = xs_visible(pos1, key, p.window);
+                const bool v2 = xs_visible(pos2, key, p.window);
                 s[i][e] = v1 ? s[i][e] * p.scale_log2 : -INFINITY;
                 s[i][2 + e] = v2 ? s[i][2 + e] * p.scale_log2 : -INFINITY;
                 mx1 = fmaxf(mx1, s[i][e]);
@@ -622,7 +622,7 @@ __global__ void __launch_bounds__(160) attention_decode_tma_kernel(const __grid_
     const int kv_len = p.kv_lens[seq];
     const int pos0 = kv_len - q_len + t0;
     const int hi = pos0 + nt;
-    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int lo = xs_first_visible(pos0, p.window);
     const int b_lo = lo / BN, nb = (hi + BN - 1) / BN - b_lo;
     const int bs = b_lo + (int)((int64_t)nb * split / p.splits);
     const int be = b_lo + (int)((int64_t)nb * (split + 1) / p.splits);
@@ -737,8 +737,8 @@ __global__ void __launch_bounds__(160) attention_decode_tma_kernel(const __grid_
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int key = key0 + i * 8 + e;
-                const bool v1 = key <= pos1 && (p.window == 0 || pos1 - key < p.window);
-                const bool v2 = key <= pos2 && (p.window == 0 || pos2 - key < p.window);
+                const bool v1 = xs_visible(pos1, key, p.window);
+                const bool v2 = xs_visible(pos2, key, p.window);
                 sc[i][e] = v1 ? sc[i][e] * p.scale_log2 : -INFINITY;
                 sc[i][2 + e] = v2 ? sc[i][2 + e] * p.scale_log2 : -INFINITY;
                 mx1 = fmaxf(mx1, sc[i][e]);
@@ -1143,7 +1143,7 @@ XS_API int xs_attention_mma_merged(const void* q, const void* pool, const int32_
     const int G = Hq / Hkv;
     XS_REQUIRE(xs_attention_mma_supports(D, page_size, G),
                "attention (tensor cores): head size %d, page size %d, group %d is not supported", D, page_size, G);
-    XS_REQUIRE(splits >= 1 && splits <= 64 && window >= 0 && max_q_len >= 1 && n_seqs >= 1 && P >= 1,
+    XS_REQUIRE(splits >= 1 && splits <= 64 && max_q_len >= 1 && n_seqs >= 1 && P >= 1,
                "attention: bad sizes (1 to 64 key splits)");
     XS_REQUIRE(n_seqs <= 65535 && (int64_t)Hkv * splits <= 65535, "attention: grid too large");
     const int64_t need = xs_attention_mma_scratch_bytes((int64_t)T * Hq, D, splits);

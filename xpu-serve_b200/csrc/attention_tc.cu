@@ -148,7 +148,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
     const int kv_len = p.kv_lens[seq];
     const int pos0 = kv_len - q_len + t0;
     const int hi = pos0 + nt;                                  // keys [lo, hi) matter to this tile
-    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int lo = xs_first_visible(pos0, p.window);
     const int b_lo = lo / TN, nb = (hi + TN - 1) / TN - b_lo;
     const int32_t* table = p.page_table + (int64_t)seq * p.P;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -306,7 +306,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
             tcgen05_fence_after();
             const int key0 = (b_lo + j) * TN;
             // a block that every row of the tile sees whole needs no test per key
-            const bool plain = pos >= 0 && key0 + TN - 1 <= pos0 && (p.window == 0 || pos0 + nt - 1 - key0 < p.window);
+            const bool plain = pos >= 0 && key0 + TN - 1 <= pos0 && key0 >= xs_first_visible(pos0 + nt - 1, p.window);
             // this row's 128 scores of the block, read once and kept through both passes
             uint32_t raw[TN];
 #pragma unroll
@@ -320,7 +320,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
 #pragma unroll
                 for (int e = 0; e < TN; ++e) {
                     const int key = key0 + e;
-                    const bool see = key <= pos && (p.window == 0 || pos - key < p.window);   // pos -1: nothing
+                    const bool see = xs_visible(pos, key, p.window);   // pos -1: nothing
                     if (!see) raw[e] = 0xff800000u;                // -inf: its weight will be exactly 0
                     mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(raw[e]));
                 }
@@ -449,7 +449,7 @@ XS_API int xs_attention_tc(const void* q, const void* pool, int64_t pool_pages, 
     const int G = Hq / Hkv;
     XS_REQUIRE(xs_attention_tc_supports(D, page_size, G),
                "attention (tcgen05): head size %d, page size %d, group %d is not supported", D, page_size, G);
-    XS_REQUIRE(window >= 0 && max_q_len >= 1 && n_seqs >= 1 && P >= 1 && pool_pages >= 1 && status != nullptr,
+    XS_REQUIRE(max_q_len >= 1 && n_seqs >= 1 && P >= 1 && pool_pages >= 1 && status != nullptr,
                "attention (tcgen05): bad sizes");
     XS_REQUIRE(n_seqs <= 65535 && Hkv <= 65535, "attention (tcgen05): grid too large");
     XS_REQUIRE((uintptr_t)q % 16 == 0 && (uintptr_t)pool % 16 == 0 && (uintptr_t)out % 16 == 0,

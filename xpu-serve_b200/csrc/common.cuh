@@ -82,6 +82,15 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
     return warp_sum(t);
 }
 
+// Which keys j <= pos a query at position pos sees, as one number: 0: all of them; W > 0: those with pos - j < W (a
+// sliding window); W < 0: those in the query's own block of -W positions, blocks counted from the sequence's position 0.
+__device__ __forceinline__ int xs_first_visible(int pos, int window) {
+    return window > 0 ? max(0, pos - window + 1) : window < 0 ? pos - pos % (-window) : 0;
+}
+__device__ __forceinline__ bool xs_visible(int pos, int key, int window) {
+    return key <= pos && key >= xs_first_visible(pos, window);
+}
+
 static inline int ceil_div_i(int64_t a, int64_t b) { return (int)((a + b - 1) / b); }
 
 // ---- programmatic dependent launch ------------------------------------------------------------

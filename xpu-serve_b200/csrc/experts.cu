@@ -65,6 +65,35 @@ __global__ void clamped_glu_bf16x8_kernel(const __nv_bfloat16* __restrict__ gu, 
     }
 }
 
+// ------------------------------------------------------------------------------------------------- squared ReLU
+// out = max(x, 0)^2, the square taken in float32.
+template <typename T>
+__global__ void relu_squared_kernel(const T* __restrict__ x, T* __restrict__ out, int64_t total) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const float v = fmaxf(to_f32(x[i]), 0.0f);
+        out[i] = from_f32<T>(v * v);
+    }
+}
+
+__global__ void relu_squared_bf16x8_kernel(const uint4* __restrict__ x, uint4* __restrict__ out, int64_t total8) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total8; i += (int64_t)gridDim.x * blockDim.x) {
+        uint4 raw = x[i];
+        __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float2 f = __bfloat1622float2(p[k]);
+            f.x = fmaxf(f.x, 0.0f);
+            f.y = fmaxf(f.y, 0.0f);
+            p[k] = __floats2bfloat162_rn(f.x * f.x, f.y * f.y);
+        }
+        out[i] = raw;
+    }
+}
+
 // ----------------------------------------------------------------------------------------------------- router logits
 // logits[t, e] = x[t] . w[e] in float32: a warp per (token, expert) pair walks both rows (16-byte loads where the rows
 // allow, eight loads in flight a lane); a lane's partial sums and the warp's reduction run in an order that depends on
@@ -105,13 +134,13 @@ __global__ void moe_logits_kernel(const T* __restrict__ x, int64_t ldx, const T*
 }
 
 // ------------------------------------------------------------------------------------------------------------ route
-__global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E, int top, int32_t* __restrict__ ids,
-                                 float* __restrict__ wts) {
+__global__ void moe_route_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, float scale,
+                                 int32_t* __restrict__ ids, float* __restrict__ wts) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x * blockDim.x + threadIdx.x;
     if (t >= T) return;
-    const float* zg = logits + (int64_t)t * E;
+    const float* zg = logits + (int64_t)t * ld;
     float zl[kLocalExperts];            // up to 64 logits are read once, all loads in flight
     if (E <= kLocalExperts) {
 #pragma unroll
@@ -143,20 +172,20 @@ __global__ void moe_route_kernel(const float* __restrict__ logits, int T, int E,
     }
     for (int k = 0; k < top; ++k) {
         ids[(int64_t)t * top + k] = chosen[k];
-        wts[(int64_t)t * top + k] = val[k] / sum;
+        wts[(int64_t)t * top + k] = val[k] / sum * scale;
     }
 }
 
 // A warp per token (E <= 256): a lane holds logits lane, lane + 32, ...; each of the `top` rounds finds the largest logit
 // left (ties: the lower index) by a reduction over the warp.
-__global__ void moe_route_warp_kernel(const float* __restrict__ logits, int T, int E, int top, int32_t* __restrict__ ids,
-                                      float* __restrict__ wts) {
+__global__ void moe_route_warp_kernel(const float* __restrict__ logits, int ld, int T, int E, int top, float scale,
+                                      int32_t* __restrict__ ids, float* __restrict__ wts) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
     const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= T) return;
-    const float* z = logits + (int64_t)t * E;
+    const float* z = logits + (int64_t)t * ld;
     float v[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = lane + 32 * j < E ? z[lane + 32 * j] : -INFINITY;
@@ -195,7 +224,7 @@ __global__ void moe_route_warp_kernel(const float* __restrict__ logits, int T, i
     }
     if (lane < top) {
         ids[(int64_t)t * top + lane] = mine_id;
-        wts[(int64_t)t * top + lane] = mine / sum;
+        wts[(int64_t)t * top + lane] = mine / sum * scale;
     }
 }
 
@@ -250,7 +279,8 @@ constexpr int TM = 64, TN = 64, TK = 32;
 template <typename TX, typename TO, bool GLU>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TX* __restrict__ x, int64_t ldx, const TX* __restrict__ w, TO* __restrict__ out, int64_t ldo,
-                const int32_t* __restrict__ source, int top, const int32_t* __restrict__ meta, int N, int K) {
+                const int32_t* __restrict__ source, int top, const int32_t* __restrict__ meta, int N, int K, float limit,
+                float alpha, float shift) {
     __shared__ float xs[TK][TM + 1];
     __shared__ float ws[GLU ? 2 : 1][TK][TN + 1];
     __shared__ int64_t src_row[TM];
@@ -326,8 +356,14 @@ moe_gemm_kernel(const TX* __restrict__ x, int64_t ldx, const TX* __restrict__ w,
             float v = acc[0][i][j];
             if (GLU) {
                 // the gate and the up product are rounded to the activation type first, as two separate products' would be
-                const float g = to_f32(from_f32<TO>(v)), u = to_f32(from_f32<TO>(acc[GLU ? 1 : 0][i][j]));
-                v = g * sigmoid_f(g) * u;
+                float g = to_f32(from_f32<TO>(v)), u = to_f32(from_f32<TO>(acc[GLU ? 1 : 0][i][j]));
+                if (limit > 0.0f) {          // the clamped unit: g = min(gate, limit), u = clamp(up, -limit, limit)
+                    g = fminf(g, limit);
+                    u = fminf(fmaxf(u, -limit), limit);
+                    v = g * sigmoid_f(alpha * g) * (u + shift);
+                } else {
+                    v = g * sigmoid_f(g) * u;
+                }
             }
             out[(int64_t)(row0 + r) * ldo + gn] = from_f32<TO>(v);
         }
@@ -350,12 +386,15 @@ __global__ void moe_gather_kernel(const uint4* __restrict__ x, int64_t ldx16, co
 // ---------------------------------------------------------------------------------------------------------- combine
 template <typename TI, typename TO>
 __global__ void moe_combine_kernel(const TI* __restrict__ rows_out, const int32_t* __restrict__ place,
-                                   const float* __restrict__ wts, TO* __restrict__ y, int H, int top) {
+                                   const float* __restrict__ wts, TO* __restrict__ y, int H, int top,
+                                   const TI* __restrict__ shared, const float* __restrict__ shared_gate, int ld_gate) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
+    // a unit that every token uses joins the sum, times sigmoid of the token's gate logit (1 without one)
+    const float sg = shared == nullptr ? 0.0f : shared_gate == nullptr ? 1.0f : sigmoid_f(shared_gate[(int64_t)t * ld_gate]);
     for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        float v = 0.0f;
+        float v = shared == nullptr ? 0.0f : sg * to_f32(shared[(int64_t)t * H + c]);
         for (int k = 0; k < top; ++k)
             v = fmaf(wts[(int64_t)t * top + k], to_f32(rows_out[(int64_t)place[(int64_t)t * top + k] * H + c]), v);
         y[(int64_t)t * H + c] = from_f32<TO>(v);
@@ -386,6 +425,22 @@ XS_API int xs_clamped_glu(const void* gu, void* out, int dtype, int T, int F, in
     return 0;
 }
 
+XS_API int xs_relu_squared(const void* x, void* out, int dtype, int64_t total, cudaStream_t stream) {
+    if (total == 0) return 0;
+    XS_REQUIRE(total > 0, "relu_squared: %lld elements", (long long)total);
+    if (dtype == XS_BF16 && total % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0) {
+        const int64_t total8 = total / 8;
+        const int blocks8 = (int)((total8 + 255) / 256 < 148 * 16 ? (total8 + 255) / 256 : 148 * 16);
+        xs_launch(relu_squared_bf16x8_kernel, dim3(blocks8), dim3(256), 0, stream, (const uint4*)x, (uint4*)out, total8);
+        XS_LAUNCH_CHECK("relu_squared");
+        return 0;
+    }
+    const int blocks = (int)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    XS_DISPATCH_DTYPE(dtype, TT, xs_launch(relu_squared_kernel<TT>, dim3(blocks), dim3(256), 0, stream, (const TT*)x, (TT*)out, total));
+    XS_LAUNCH_CHECK("relu_squared");
+    return 0;
+}
+
 XS_API int xs_moe_logits(const void* x, int64_t ldx, const void* w, float* logits, int T, int E, int K, int dtype,
                          cudaStream_t stream) {
     if (T == 0) return 0;
@@ -398,14 +453,18 @@ XS_API int xs_moe_logits(const void* x, int64_t ldx, const void* w, float* logit
     return 0;
 }
 
-XS_API int xs_moe_route(const float* logits, int T, int E, int top, int32_t* ids, float* wts, cudaStream_t stream) {
+// logits: rows of `ld` >= E floats, of which the first E are the experts' (a caller may keep other per-token numbers behind
+// them). The weights are the softmax over the chosen logits (which is the softmax over all of them, divided by the chosen
+// ones' sum) times `scale`.
+XS_API int xs_moe_route(const float* logits, int ld, int T, int E, int top, float scale, int32_t* ids, float* wts,
+                        cudaStream_t stream) {
     if (T == 0) return 0;
-    XS_REQUIRE(T > 0 && E > 0 && top > 0 && top <= E && top <= kMaxTop, "moe_route: %d tokens, %d experts, top %d (at most %d)",
-               T, E, top, kMaxTop);
+    XS_REQUIRE(T > 0 && E > 0 && top > 0 && top <= E && top <= kMaxTop && ld >= E,
+               "moe_route: %d tokens, %d experts (row stride %d), top %d (at most %d)", T, E, ld, top, kMaxTop);
     if (E <= 256 && E > top)
-        xs_launch(moe_route_warp_kernel, dim3(ceil_div_i(T, 4)), dim3(128), 0, stream, logits, T, E, top, ids, wts);
+        xs_launch(moe_route_warp_kernel, dim3(ceil_div_i(T, 4)), dim3(128), 0, stream, logits, ld, T, E, top, scale, ids, wts);
     else
-        xs_launch(moe_route_kernel, dim3(ceil_div_i(T, 32)), dim3(32), 0, stream, logits, T, E, top, ids, wts);
+        xs_launch(moe_route_kernel, dim3(ceil_div_i(T, 32)), dim3(32), 0, stream, logits, ld, T, E, top, scale, ids, wts);
     XS_LAUNCH_CHECK("moe_route");
     return 0;
 }
@@ -431,10 +490,11 @@ XS_API int xs_moe_plan(const int32_t* ids, int n, int E, int tile_rows, int rows
     return 0;
 }
 
-// x and w share an element type; out is float32 or that type. glu: w is [E, 2 N, K] and out = silu(gate) * up.
+// x and w share an element type; out is float32 or that type. glu: w is [E, 2 N, K] and out = silu(gate) * up, or with
+// limit > 0 the clamped unit's g * sigmoid(alpha g) * (u + shift), g = min(gate, limit), u = clamp(up, -limit, limit).
 XS_API int xs_moe_gemm(const void* x, int64_t ldx, const void* w, void* out, int64_t ldo, const int32_t* source, int top,
-                       const int32_t* meta, int max_tiles, int N, int K, int glu, int in_dtype, int out_dtype,
-                       cudaStream_t stream) {
+                       const int32_t* meta, int max_tiles, int N, int K, int glu, float limit, float alpha, float shift,
+                       int in_dtype, int out_dtype, cudaStream_t stream) {
     if (max_tiles == 0) return 0;
     XS_REQUIRE(max_tiles > 0 && max_tiles <= 65535 && N > 0 && K > 0 && top > 0, "moe_gemm: %d tiles, N %d, K %d", max_tiles, N, K);
     XS_REQUIRE(in_dtype == out_dtype, "moe_gemm: element types in %d, out %d", in_dtype, out_dtype);
@@ -443,10 +503,10 @@ XS_API int xs_moe_gemm(const void* x, int64_t ldx, const void* w, void* out, int
     do {                                                                                                            \
         if (glu)                                                                                                    \
             xs_launch(moe_gemm_kernel<TT, TT, true>, grid, dim3(256), 0, stream, (const TT*)x, ldx, (const TT*)w,   \
-                      (TT*)out, ldo, source, top, meta, N, K);                                                      \
+                      (TT*)out, ldo, source, top, meta, N, K, limit, alpha, shift);                                                      \
         else                                                                                                        \
             xs_launch(moe_gemm_kernel<TT, TT, false>, grid, dim3(256), 0, stream, (const TT*)x, ldx, (const TT*)w,  \
-                      (TT*)out, ldo, source, top, meta, N, K);                                                      \
+                      (TT*)out, ldo, source, top, meta, N, K, limit, alpha, shift);                                                      \
     } while (0)
     XS_DISPATCH_DTYPE(in_dtype, TT, XS_GO(TT));
 #undef XS_GO
@@ -467,12 +527,12 @@ XS_API int xs_moe_gather(const void* x, int64_t ldx, const int32_t* source, int 
 }
 
 XS_API int xs_moe_combine(const void* rows_out, const int32_t* place, const float* wts, void* y, int T, int H, int top,
-                          int dtype, cudaStream_t stream) {
+                          const void* shared, const float* shared_gate, int ld_gate, int dtype, cudaStream_t stream) {
     if (T == 0) return 0;
     XS_REQUIRE(T > 0 && H > 0 && top > 0, "moe_combine: %d tokens of %d, top %d", T, H, top);
     XS_DISPATCH_DTYPE(dtype, TT,
                       xs_launch(moe_combine_kernel<TT, TT>, dim3(T), dim3(H >= 1024 ? 256 : 128), 0, stream,
-                                (const TT*)rows_out, place, wts, (TT*)y, H, top));
+                                (const TT*)rows_out, place, wts, (TT*)y, H, top, (const TT*)shared, shared_gate, ld_gate));
     XS_LAUNCH_CHECK("moe_combine");
     return 0;
 }

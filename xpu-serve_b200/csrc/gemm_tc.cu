@@ -965,8 +965,8 @@ XS_API int xs_gemm_tc_clamped(const void* x, const void* w, void* out, int out_d
 // experts' weights one under another; out: [rows_cap, N] (N / 2 with the SwiGLU epilogue, whose weight is stacked in
 // blocks of 8 gate and 8 up rows per expert). max_m_tiles: the most tiles the plan can hold (the grid's bound).
 XS_API int xs_gemm_tc_grouped(const void* x, const void* w, void* out, int out_dtype, int epilogue, const int32_t* meta,
-                              int max_m_tiles, int rows_cap, int E, int N, int K, int64_t ldx, int64_t ldo, int* status,
-                              cudaStream_t stream) {
+                              int max_m_tiles, int rows_cap, int E, int N, int K, int64_t ldx, int64_t ldo, float glu_limit,
+                              float glu_alpha, float glu_shift, int* status, cudaStream_t stream) {
     if (max_m_tiles == 0 || N == 0) return 0;
     XS_REQUIRE(xs_gemm_tc_supports(rows_cap, N, K, ldx, K), "gemm (tcgen05, grouped): rows %d, N %d, K %d, stride %lld not supported",
                rows_cap, N, K, (long long)ldx);
@@ -984,7 +984,8 @@ XS_API int xs_gemm_tc_grouped(const void* x, const void* w, void* out, int out_d
     p.status = status;
     p.T = rows_cap; p.N = N; p.K = K; p.ksplit = 1; p.epilogue = epilogue; p.out_f32 = out_dtype == XS_F32;
     p.ldo = ldo;
-    p.glu_limit = 0.0f; p.glu_alpha = 1.0f; p.glu_shift = 0.0f;
+    // (the gated epilogue's activation: limit 0 is silu(gate) * up, limit > 0 the clamped unit's)
+    p.glu_limit = glu_limit; p.glu_alpha = glu_alpha; p.glu_shift = glu_shift;
     const int esz = p.out_f32 ? 4 : 2;
     p.vec = ((uintptr_t)out % 16 == 0) && ((ldo * esz) % 16 == 0);
     alignas(64) CUtensorMap mw, mx;

@@ -172,9 +172,10 @@ __global__ void add_layernorm_vec_kernel(float* __restrict__ h, const TM* __rest
 
 // y[t, g, :] = x[t, g, :] / sqrt(mean(x[t, g, :]^2) + eps) * w[g, :]: a unit-RMS norm in `groups` equal parts of a
 // row (x float32, y in the activation type). One block per (row, part).
+// With `gate` (rows of the activation type, `ld_gate` apart): y is also multiplied by sigmoid(gate[t, g, :]).
 template <typename TY>
 __global__ void grouped_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ w, TY* __restrict__ y,
-                                       int width, int part, float eps) {
+                                       int width, int part, float eps, const TY* __restrict__ gate, int64_t ld_gate) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
@@ -184,6 +185,12 @@ __global__ void grouped_rmsnorm_kernel(const float* __restrict__ x, const float*
     for (int c = threadIdx.x; c < part; c += blockDim.x) ss += xr[c] * xr[c];
     const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)part + eps);
     const float* wr = w + (int64_t)blockIdx.y * part;
+    if (gate != nullptr) {
+        const TY* gr = gate + (int64_t)blockIdx.x * ld_gate + (int64_t)blockIdx.y * part;
+        for (int c = threadIdx.x; c < part; c += blockDim.x)
+            y[base + c] = from_f32<TY>(xr[c] * inv * wr[c] / (1.0f + expf(-to_f32(gr[c]))));
+        return;
+    }
     for (int c = threadIdx.x; c < part; c += blockDim.x) y[base + c] = from_f32<TY>(xr[c] * inv * wr[c]);
 }
 
@@ -234,7 +241,7 @@ XS_API int xs_add_layernorm(float* h, const void* m, int m_dtype, const float* p
 }
 
 XS_API int xs_grouped_rmsnorm(const float* x, const float* w, void* y, int y_dtype, int rows, int width, int groups,
-                              float eps, cudaStream_t stream) {
+                              float eps, const void* gate, int64_t ld_gate, cudaStream_t stream) {
     if (rows == 0) return 0;
     XS_REQUIRE(rows > 0 && width > 0 && groups > 0 && width % groups == 0, "grouped_rmsnorm: %d rows of %d in %d parts",
                rows, width, groups);
@@ -243,7 +250,7 @@ XS_API int xs_grouped_rmsnorm(const float* x, const float* w, void* y, int y_dty
     const int threads = part >= 1024 ? 256 : 128;
     XS_DISPATCH_DTYPE(y_dtype, TY,
                       xs_launch(grouped_rmsnorm_kernel<TY>, dim3(rows, groups), dim3(threads), 0, stream, x, w, (TY*)y,
-                                width, part, eps));
+                                width, part, eps, (const TY*)gate, ld_gate));
     XS_LAUNCH_CHECK("grouped_rmsnorm");
     return 0;
 }

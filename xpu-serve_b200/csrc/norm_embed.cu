@@ -44,6 +44,60 @@ __global__ void embed_kernel(const TW* __restrict__ table, const int32_t* __rest
     for (int c = threadIdx.x; c < H; c += blockDim.x) out[c] = to_f32(row[c]) * scale;
 }
 
+// A token's row plus a row of a second table chosen by a hash of the previous and the current token, plus a sine/cosine
+// vector of the position, then an RMS norm (w == nullptr: none):
+//     x = table[tok] * scale + pair[pos == 0 ? buckets : (prev * mul_prev + tok * mul_cur) mod buckets]
+//     x[2 i] += sin(pos f_i),  x[2 i + 1] += cos(pos f_i)          (inv_freq holds the f_i in float32; the angle is float32)
+//     h = x / sqrt(mean(x^2) + eps) * w
+// The previous token of a step's first token of a sequence is what `last_token[slot]` holds; the block of that token then
+// writes the sequence's last token of this step there, so the word is read before it is written whatever the order of blocks.
+template <typename TW>
+__global__ void embed_pair_kernel(const TW* __restrict__ table, const TW* __restrict__ pair, const int32_t* __restrict__ ids,
+                                  const int32_t* __restrict__ positions, const int32_t* __restrict__ seq_of_token,
+                                  const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ slots,
+                                  int32_t* __restrict__ last_token, const float* __restrict__ inv_freq,
+                                  const float* __restrict__ w, float* __restrict__ h, int H, float scale, int buckets,
+                                  long long mul_prev, long long mul_cur, float eps) {
+    extern __shared__ float row[];
+    __shared__ float scratch[32];
+    __shared__ int prev_s;
+    pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int seq = seq_of_token[t], pos = positions[t], tok = ids[t];
+    const int first = cu_seqlens[seq], end = cu_seqlens[seq + 1];
+    pdl_wait();
+    if (threadIdx.x == 0) {
+        int prev = 0;
+        if (t == first) {
+            const int slot = slots[seq];
+            prev = last_token[slot];
+            last_token[slot] = ids[end - 1];
+        } else {
+            prev = ids[t - 1];
+        }
+        prev_s = prev;
+    }
+    __syncthreads();
+    const long long bucket = pos == 0 ? (long long)buckets : ((long long)prev_s * mul_prev + (long long)tok * mul_cur) % buckets;
+    const TW* er = table + (int64_t)tok * H;
+    const TW* pr = pair + bucket * H;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < H; c += blockDim.x) {
+        const float angle = (float)pos * inv_freq[c >> 1];
+        const float v = to_f32(er[c]) * scale + to_f32(pr[c]) + ((c & 1) ? cosf(angle) : sinf(angle));
+        row[c] = v;
+        ss += v * v;
+    }
+    float* out = h + (int64_t)t * H;
+    if (w == nullptr) {
+        for (int c = threadIdx.x; c < H; c += blockDim.x) out[c] = row[c];
+        return;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)H + eps);
+    for (int c = threadIdx.x; c < H; c += blockDim.x) out[c] = row[c] * inv * w[c];
+}
+
 // logits = cap * tanh(logits / cap), in place: a soft limit that some architectures put on their logits.
 __global__ void logit_cap_kernel(float* __restrict__ logits, int64_t n, float cap, float inv_cap) {
     pdl_launch_dependents();
@@ -62,6 +116,28 @@ XS_API int xs_embed(const void* table, int table_dtype, const int32_t* ids, floa
     return 0;
 }
 
+XS_API int xs_embed_pair(const void* table, const void* pair, int table_dtype, const int32_t* ids, const int32_t* positions,
+                         const int32_t* seq_of_token, const int32_t* cu_seqlens, const int32_t* slots, int32_t* last_token,
+                         const float* inv_freq, const float* w, float* h, int T, int H, float scale, int buckets,
+                         long long mul_prev, long long mul_cur, float eps, cudaStream_t stream) {
+    if (T == 0) return 0;
+    XS_REQUIRE(T > 0 && H > 0 && buckets > 0 && mul_prev >= 0 && mul_cur >= 0, "embed_pair: %d tokens of width %d, %d buckets", T, H, buckets);
+    XS_REQUIRE((size_t)H * 4 <= 200 * 1024, "embed_pair: width %d does not fit shared memory (limit 51200)", H);
+    const size_t smem = (size_t)H * sizeof(float);
+#define XS_GO(TW)                                                                                                          \
+    do {                                                                                                                   \
+        if (smem > 48 * 1024)                                                                                              \
+            cudaFuncSetAttribute(embed_pair_kernel<TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);           \
+        xs_launch(embed_pair_kernel<TW>, dim3(T), dim3(H >= 2048 ? 512 : 256), smem, stream, (const TW*)table,             \
+                  (const TW*)pair, ids, positions, seq_of_token, cu_seqlens, slots, last_token, inv_freq, w, h, H, scale,  \
+                  buckets, mul_prev, mul_cur, eps);                                                                        \
+    } while (0)
+    XS_DISPATCH_DTYPE(table_dtype, TW, XS_GO(TW));
+#undef XS_GO
+    XS_LAUNCH_CHECK("embed_pair");
+    return 0;
+}
+
 XS_API int xs_logit_cap(float* logits, int64_t n, float cap, cudaStream_t stream) {
     if (n == 0) return 0;
     XS_REQUIRE(n > 0 && cap > 0.0f, "logit cap: %lld values, cap %g", (long long)n, (double)cap);
@@ -77,6 +153,7 @@ XS_API int xs_logit_cap(float* logits, int64_t n, float cap, cudaStream_t stream
 //   if m:      b = m[r];  if post_w: b = RMSNorm(b, post_w, eps_post)
 //              v = v + b;  h[r] = v            the residual sum stays float32
 //   if w:      y[i] = RMSNorm(v, w, eps)       written in y's element type
+//   else if y: y[i] = v                        (a layer whose sublayers read the stream itself)
 // One block per row; the row lives in shared memory between the passes.
 template <typename TM, typename TY>
 __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TM* __restrict__ m,
@@ -122,7 +199,15 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ h, const TM* __restrict__
             ss += v * v;
         }
     }
-    if (w == nullptr) return;
+    if (w == nullptr) {
+        // no norm reads the stream: y (when given) is the sum itself in y's element type
+        if (y != nullptr) {
+            __syncthreads();
+            TY* yc = y + (int64_t)i * H;
+            for (int c = threadIdx.x; c < H; c += blockDim.x) yc[c] = from_f32<TY>(row[c]);
+        }
+        return;
+    }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)H + eps);
     TY* yr = y + (int64_t)i * H;
@@ -207,7 +292,17 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ h, const TM* __restri
             store4(hr + 4 * c, v[k]);
         }
     }
-    if (w == nullptr) return;
+    if (w == nullptr) {
+        if (y != nullptr) {
+            TY* yc = y + (int64_t)i * H;
+#pragma unroll
+            for (int k = 0; k < NV; ++k) {
+                const int c = threadIdx.x + k * blockDim.x;
+                if (c < chunks) store4(yc + 4 * c, v[k]);
+            }
+        }
+        return;
+    }
 #pragma unroll
     for (int k = 0; k < NV; ++k) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
     ss = block_sum(ss, scratch);

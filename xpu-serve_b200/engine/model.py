@@ -93,6 +93,10 @@ class Model:
         for layer in spec.layers:
             own = {k[len(layer.prefix):]: v for k, v in weights.items() if k.startswith(layer.prefix)}
             self.blocks.append(registry.arrangement_class(layer.kind)(layer, own, rt))
+        # an embedding that is more than a table lookup is a part of its own; what it keeps per sequence is the cache's
+        # last view, behind the layer calls'
+        self.embedding = (registry.embedding_class(spec.embedding.kind)(spec.embedding, weights, rt, self.embed)
+                          if spec.embedding is not None else None)
         self.stager = StepStager(rt.device)
         # Decode steps are launch-bound (some 150 small kernels): they are captured once per batch
         # size into a CUDA graph and replayed. XS_NO_GRAPHS=1 runs every step kernel by kernel.
@@ -117,6 +121,7 @@ class Model:
             registry.norm_class(layer.norm.kind),
             *([registry.ffn_class(layer.ffn.kind)] if layer.ffn is not None else [])))
         parts_ok = parts_ok and getattr(registry.norm_class(spec.final_norm.kind), "fixed_shape_ok", False)
+        parts_ok = parts_ok and (self.embedding is None or getattr(self.embedding, "fixed_shape_ok", False))
         self.use_prompt_graphs = self.use_graphs and parts_ok and os.environ.get("XS_NO_PROMPT_GRAPHS", "0") != "1"
         self._prompt_graphs: Dict[int, Dict[int, _DecodeGraph]] = {}
         self.last_h2d_bytes = 0      # bytes of the last step's description copied to the device
@@ -128,6 +133,9 @@ class Model:
             layer = self.spec.layers[call.layer]
             needs.append(registry.arrangement_class(layer.kind).cache_need(layer))
             shares.append(call.cache_of)
+        if self.spec.embedding is not None:
+            needs.append(registry.embedding_class(self.spec.embedding.kind).cache_need(self.spec.embedding))
+            shares.append(None)
         return needs, shares
 
     def new_cache(self, max_tokens: int, max_slots: Optional[int] = None,
@@ -364,7 +372,10 @@ class Model:
         token (a soft cap on the logits keeps their order, so it does not matter that it comes after)."""
         rt, spec = self.rt, self.spec
         h = rt.ws.get("stream", (ctx.n_tokens, spec.hidden), torch.float32)
-        ops.embed(self.embed, ctx.tokens, h, spec.embed_scale)
+        if self.embedding is not None:
+            self.embedding.forward(ctx, cache.views[len(spec.order)], h)
+        else:
+            ops.embed(self.embed, ctx.tokens, h, spec.embed_scale)
         stream = ResidualStream(h, rt)
         last = len(spec.order) - 1
         for i, call in enumerate(spec.order):

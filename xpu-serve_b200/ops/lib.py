@@ -54,16 +54,19 @@ def _signatures(lib) -> None:
         "xs_apply_penalties": [P, L, I, I, P, P, P, P, P, P, P],
         "xs_note_tokens": [P, P, I, I, P, P, I, P],
         "xs_add_layernorm": [P, P, I, P, P, P, I, P, I, I, F, F, P],
-        "xs_grouped_rmsnorm": [P, P, P, I, I, I, I, F, P],
+        "xs_grouped_rmsnorm": [P, P, P, I, I, I, I, F, P, L, P],
         "xs_clamped_glu": [P, P, I, I, I, L, F, F, F, I, P],
         "xs_gemm_tc_clamped": [P, P, P, I, I, I, I, L, L, L, F, F, F, P, P],
-        "xs_moe_route": [P, I, I, I, P, P, P],
+        "xs_moe_route": [P, I, I, I, I, F, P, P, P],
         "xs_moe_logits": [P, L, P, P, I, I, I, I, P],
         "xs_moe_plan": [P, I, I, I, I, P, P, P, P],
         "xs_moe_gather": [P, L, P, I, P, I, I, P],
-        "xs_gemm_tc_grouped": [P, P, P, I, I, P, I, I, I, I, I, L, L, P, P],
-        "xs_moe_gemm": [P, L, P, P, L, P, I, P, I, I, I, I, I, I, P],
-        "xs_moe_combine": [P, P, P, P, I, I, I, I, P],
+        "xs_gemm_tc_grouped": [P, P, P, I, I, P, I, I, I, I, I, L, L, F, F, F, P, P],
+        "xs_moe_gemm": [P, L, P, P, L, P, I, P, I, I, I, I, F, F, F, I, I, P],
+        "xs_moe_combine": [P, P, P, P, I, I, I, P, P, I, I, P],
+        "xs_relu_squared": [P, P, I, L, P],
+        "xs_embed_pair": [P, P, I, P, P, P, P, P, P, P, P, P, I, I, F, I, ctypes.c_longlong, ctypes.c_longlong, F, P],
+        "xs_mlstm_scan": [P, L, I, I, I, P, L, P, P, P, P, P, P, P, I, I, I, I, F, F, I, P],
         "xs_latent_prepare": [P, L, P, L, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, I, P],
         "xs_latent_attention_generic": [P, L, L, P, P, P, I, P, P, P, L, P, P, L, L, I, I, I, I, I, F, I, I, P],
         "xs_gemm_batched": [P, L, L, P, L, L, P, L, L, I, I, I, I, I, P],
@@ -790,13 +793,17 @@ def add_layernorm(h: torch.Tensor, m: Optional[torch.Tensor], post_w: Optional[t
                                    float(eps if eps_post is None else eps_post), float(eps), _stream()))
 
 
-def grouped_rmsnorm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, groups: int, eps: float) -> None:
-    """y[t, g] = x[t, g] / sqrt(mean(x[t, g]^2) + eps) * w[g] for the `groups` equal parts g of a row; x float32."""
+def grouped_rmsnorm(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, groups: int, eps: float,
+                    gate: Optional[torch.Tensor] = None) -> None:
+    """y[t, g] = x[t, g] / sqrt(mean(x[t, g]^2) + eps) * w[g] for the `groups` equal parts g of a row; x float32.
+    `gate` (y's element type, rows at least as wide as x's, contiguous columns): y is also multiplied by sigmoid(gate)."""
     _need(x, "x", torch.float32); _need(w, "w", torch.float32); _need(y, "y")
     if y.shape != x.shape or w.numel() != x.shape[1]:
         raise KernelError(f"grouped_rmsnorm: x {tuple(x.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
+    if gate is not None and (gate.dtype != y.dtype or gate.stride(1) != 1 or gate.shape[0] != x.shape[0] or gate.shape[1] < x.shape[1]):
+        raise KernelError(f"grouped_rmsnorm: gate {tuple(gate.shape)} {gate.dtype} for y {tuple(y.shape)} {y.dtype}")
     _check(load().xs_grouped_rmsnorm(x.data_ptr(), w.data_ptr(), y.data_ptr(), _code(y), x.shape[0], x.shape[1],
-                                     int(groups), float(eps), _stream()))
+                                     int(groups), float(eps), _ptr(gate), 0 if gate is None else gate.stride(0), _stream()))
 
 
 def clamped_glu(gu: torch.Tensor, out: torch.Tensor, limit: float, alpha: float, shift: float, interleave: int = 0) -> None:
@@ -844,13 +851,16 @@ def moe_logits(x: torch.Tensor, w: torch.Tensor, logits: torch.Tensor) -> None:
     _check(load().xs_moe_logits(x.data_ptr(), x.stride(0), w.data_ptr(), logits.data_ptr(), T, E, K, _code(x), _stream()))
 
 
-def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, wts: torch.Tensor) -> None:
-    """Per row of float32 logits: the `top` largest (ties: the lower index) into ids, their softmax into wts."""
+def moe_route(logits: torch.Tensor, top: int, ids: torch.Tensor, wts: torch.Tensor, experts: Optional[int] = None,
+              scale: float = 1.0) -> None:
+    """Per row of float32 logits: the `top` largest (ties: the lower index) into ids, their softmax times `scale` into
+    wts. `experts`: only the first so many columns of a row are router logits (default: all)."""
     _need(logits, "router logits", torch.float32); _need(ids, "ids", torch.int32); _need(wts, "weights", torch.float32)
-    T, E = logits.shape
+    T, ld = logits.shape
+    E = ld if experts is None else int(experts)
     if ids.numel() < T * top or wts.numel() < T * top:
         raise KernelError(f"moe_route: {T} tokens x top {top} do not fit ids {ids.numel()} / weights {wts.numel()}")
-    _check(load().xs_moe_route(logits.data_ptr(), T, E, int(top), ids.data_ptr(), wts.data_ptr(), _stream()))
+    _check(load().xs_moe_route(logits.data_ptr(), ld, T, E, int(top), float(scale), ids.data_ptr(), wts.data_ptr(), _stream()))
 
 
 def moe_max_tiles_of(rows: int, experts: int, tile_rows: int) -> int:
@@ -882,10 +892,13 @@ def moe_gather(x: torch.Tensor, source: torch.Tensor, top: int, sorted_rows: tor
                                 sorted_rows.shape[0], x.shape[1], _stream()))
 
 
-def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch.Tensor, max_tiles: int, glu: bool) -> None:
+def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch.Tensor, max_tiles: int, glu: bool,
+                    clamp=None) -> None:
     """out[r] = w[expert of r's tile] . x[r] on tcgen05 tensor cores for the padded row tiles (128 rows) of a plan.
     w: [experts, N, K] bfloat16; with `glu` each expert's rows come in blocks of 8 gate and 8 up rows and
-    out[r] = silu(gate) * up has N / 2 columns."""
+    out[r] = silu(gate) * up has N / 2 columns; `clamp` (limit, alpha, shift): the clamped unit's activation instead,
+    g * sigmoid(alpha g) * (u + shift) with g = min(gate, limit), u = clamp(up, -limit, limit)."""
+    limit, alpha, shift = (0.0, 1.0, 0.0) if clamp is None else clamp
     _need(x, "x", torch.bfloat16); _need(w, "expert weights", torch.bfloat16); _need(out, "out", torch.bfloat16)
     E, N, K = w.shape
     if x.shape[1] != K or out.shape[0] != x.shape[0] or out.shape[1] != (N // 2 if glu else N) or x.shape[0] < 128 * max_tiles:
@@ -893,13 +906,15 @@ def gemm_tc_grouped(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: t
     mark_bounded(x.device)
     _check(load().xs_gemm_tc_grouped(x.data_ptr(), w.data_ptr(), out.data_ptr(), _code(out), EPI_SWIGLU if glu else EPI_STORE,
                                      meta.data_ptr(), int(max_tiles), x.shape[0], E, N, K, x.stride(0), out.stride(0),
-                                     gemm_tc_status(x.device).data_ptr(), _stream()))
+                                     float(limit), float(alpha), float(shift), gemm_tc_status(x.device).data_ptr(), _stream()))
 
 
 def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch.Tensor, rows: int, source: Optional[torch.Tensor],
-             top: int, glu: bool) -> None:
+             top: int, glu: bool, clamp=None) -> None:
     """out[place] = w[expert of place] . x[source[place] // top] (x[place] without `source`) for the `rows` sorted
-    places of a plan. w: [experts, N, K], or [experts, 2 N, K] with `glu` (gate rows first; out = silu(gate) * up)."""
+    places of a plan. w: [experts, N, K], or [experts, 2 N, K] with `glu` (gate rows first; out = silu(gate) * up, or
+    with `clamp` (limit, alpha, shift) the clamped unit's activation)."""
+    limit, alpha, shift = (0.0, 1.0, 0.0) if clamp is None else clamp
     for t, name in ((x, "x"), (out, "out")):
         if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1:
             raise KernelError(f"moe_gemm: {name} must be a CUDA matrix with contiguous rows")
@@ -910,15 +925,91 @@ def moe_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, meta: torch.Te
     if x.shape[1] != K or out.shape[1] != N or out.shape[0] < rows or out.dtype != x.dtype:
         raise KernelError(f"moe_gemm: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
     _check(load().xs_moe_gemm(x.data_ptr(), x.stride(0), w.data_ptr(), out.data_ptr(), out.stride(0), _ptr(source), int(top),
-                              meta.data_ptr(), moe_max_tiles(rows, E), N, K, 1 if glu else 0, _code(x), _code(out), _stream()))
+                              meta.data_ptr(), moe_max_tiles(rows, E), N, K, 1 if glu else 0, float(limit), float(alpha), float(shift),
+                              _code(x), _code(out), _stream()))
 
 
-def moe_combine(rows_out: torch.Tensor, place: torch.Tensor, wts: torch.Tensor, y: torch.Tensor, top: int) -> None:
-    """y[t] = sum_k wts[t, k] * rows_out[place[t, k]], summed in float32 in the order of k."""
+def moe_combine(rows_out: torch.Tensor, place: torch.Tensor, wts: torch.Tensor, y: torch.Tensor, top: int,
+                shared: Optional[torch.Tensor] = None, shared_gate: Optional[torch.Tensor] = None) -> None:
+    """y[t] = sum_k wts[t, k] * rows_out[place[t, k]], summed in float32 in the order of k. `shared` [T, H] (a unit that
+    every token uses) starts the sum, times sigmoid(shared_gate[t, 0]) when `shared_gate` (float32, one row a token whose
+    first column is the gate's logit) is given."""
     _need(rows_out, "expert outputs", y.dtype); _need(y, "y")
     T, H = y.shape
+    ld_gate = 0
+    if shared is not None:
+        _need(shared, "shared unit's output", y.dtype)
+        if tuple(shared.shape) != (T, H):
+            raise KernelError(f"moe_combine: shared {tuple(shared.shape)} for y {tuple(y.shape)}")
+        if shared_gate is not None:
+            if shared_gate.dtype != torch.float32 or shared_gate.dim() != 2 or shared_gate.shape[0] != T or shared_gate.stride(1) != 1:
+                raise KernelError(f"moe_combine: gate logits {tuple(shared_gate.shape)} {shared_gate.dtype} for {T} tokens")
+            ld_gate = shared_gate.stride(0)
     _check(load().xs_moe_combine(rows_out.data_ptr(), place.data_ptr(), wts.data_ptr(), y.data_ptr(), T, H, int(top),
-                                 _code(y), _stream()))
+                                 _ptr(shared), _ptr(shared_gate) if shared is not None else None, ld_gate, _code(y), _stream()))
+
+
+def relu_squared(x: torch.Tensor, out: torch.Tensor) -> None:
+    """out = max(x, 0)^2, elementwise."""
+    _need(x, "x"); _need(out, "out", x.dtype)
+    if out.shape != x.shape:
+        raise KernelError(f"relu_squared: x {tuple(x.shape)}, out {tuple(out.shape)}")
+    _check(load().xs_relu_squared(x.data_ptr(), out.data_ptr(), _code(x), x.numel(), _stream()))
+
+
+def embed_pair(table: torch.Tensor, pair: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor, seq_of_token: torch.Tensor,
+               cu_seqlens: torch.Tensor, slots: torch.Tensor, last_token: torch.Tensor, inv_freq: torch.Tensor,
+               norm_w: Optional[torch.Tensor], h: torch.Tensor, scale: float, buckets: int, mul_prev: int, mul_cur: int,
+               eps: float) -> None:
+    """h[t] = RMSNorm(table[tok] * scale + pair[bucket of (previous token, tok)] + sine/cosine of the position, norm_w)
+    in float32 (no norm without norm_w). bucket = (prev * mul_prev + tok * mul_cur) mod buckets, and row `buckets` for a
+    sequence's first token. `last_token` (int32, one word a slot) holds each sequence's last token between steps: it is
+    read for a step's first token of a sequence and then takes the sequence's last token of this step.
+    inv_freq: ceil(width / 2) float32 frequencies; entries 2i and 2i + 1 of a row get sin and cos of position * inv_freq[i]."""
+    _need(table, "embedding table"); _need(pair, "pair table", table.dtype); _need(ids, "ids", torch.int32)
+    _need(h, "h", torch.float32); _need(last_token, "last tokens", torch.int32); _need(inv_freq, "frequencies", torch.float32)
+    T, H = h.shape
+    if table.shape[1] != H or tuple(pair.shape) != (buckets + 1, H) or inv_freq.numel() < (H + 1) // 2:
+        raise KernelError(f"embed_pair: table {tuple(table.shape)}, pair table {tuple(pair.shape)} for {buckets} buckets, width {H}")
+    if norm_w is not None:
+        _need(norm_w, "norm weight", torch.float32)
+        if norm_w.numel() != H:
+            raise KernelError(f"embed_pair: norm weight of {norm_w.numel()} for width {H}")
+    _check(load().xs_embed_pair(table.data_ptr(), pair.data_ptr(), _code(table), ids.data_ptr(), positions.data_ptr(),
+                                seq_of_token.data_ptr(), cu_seqlens.data_ptr(), slots.data_ptr(), last_token.data_ptr(),
+                                inv_freq.data_ptr(), _ptr(norm_w), h.data_ptr(), T, H, float(scale), int(buckets),
+                                int(mul_prev), int(mul_cur), float(eps), _stream()))
+
+
+def mlstm_copies(vdim: int) -> int:
+    """How many copies of a head's n and m the recurrence kernel keeps (one per block of value columns)."""
+    return int(load().xs_mlstm_copies(int(vdim)))
+
+
+def mlstm_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, gates: torch.Tensor, i_bias: torch.Tensor,
+               f_bias: torch.Tensor, s_state: torch.Tensor, nm_state: torch.Tensor, cu_seqlens: torch.Tensor,
+               slots: torch.Tensor, y: torch.Tensor, heads: int, dim: int, vdim: int, cap: float, q_scale: float) -> None:
+    """The mLSTM recurrence over a step's tokens, sequence by sequence from each slot's state (csrc/mlstm.cu). qkv: rows
+    with q [heads * dim] at column q_col, k at k_col, v [heads * vdim] at v_col; gates: float32 rows [input gates' |
+    forget gates'] pre-activations without biases; s_state [slots, heads, dim, vdim], nm_state [slots, heads,
+    mlstm_copies(vdim), dim + 1] float32; y [T, heads * vdim] float32."""
+    _need(gates, "gates", torch.float32); _need(y, "y", torch.float32); _need(s_state, "state", torch.float32)
+    _need(nm_state, "normaliser state", torch.float32); _need(i_bias, "input gate bias", torch.float32)
+    _need(f_bias, "forget gate bias", torch.float32)
+    if not qkv.is_cuda or qkv.dim() != 2 or qkv.stride(1) != 1:
+        raise KernelError("mlstm: qkv must be a CUDA matrix with contiguous rows")
+    T = qkv.shape[0]
+    if (max(q_col, k_col) + heads * dim > qkv.shape[1] or v_col + heads * vdim > qkv.shape[1] or gates.shape[0] != T
+            or gates.shape[1] < 2 * heads or tuple(y.shape) != (T, heads * vdim)):
+        raise KernelError(f"mlstm: qkv {tuple(qkv.shape)}, gates {tuple(gates.shape)}, y {tuple(y.shape)} for {heads} heads of {dim} / {vdim}")
+    if tuple(s_state.shape[1:]) != (heads, dim, vdim) or tuple(nm_state.shape[1:]) != (heads, mlstm_copies(vdim), dim + 1):
+        raise KernelError(f"mlstm: state {tuple(s_state.shape)} / {tuple(nm_state.shape)} for {heads} heads of {dim} / {vdim}")
+    if i_bias.numel() != heads or f_bias.numel() != heads:
+        raise KernelError(f"mlstm: gate biases of {i_bias.numel()} / {f_bias.numel()} for {heads} heads")
+    _check(load().xs_mlstm_scan(qkv.data_ptr(), qkv.stride(0), int(q_col), int(k_col), int(v_col), gates.data_ptr(),
+                                gates.stride(0), i_bias.data_ptr(), f_bias.data_ptr(), s_state.data_ptr(), nm_state.data_ptr(),
+                                cu_seqlens.data_ptr(), slots.data_ptr(), y.data_ptr(), cu_seqlens.numel() - 1, heads, dim, vdim,
+                                float(cap), float(q_scale), _code(qkv), _stream()))
 
 
 # ----------------------------------------------------------------------------- latent attention

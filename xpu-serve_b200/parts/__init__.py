@@ -8,9 +8,12 @@ from .short_conv import ShortConvMixer
 from .swiglu import SwiGLU
 from .latent_attention import LatentAttentionMixer
 from .mamba2 import Mamba2Mixer
-from .gated_units import ClampedGLU, RoutedExperts
-from .block import Block, ResidualStream
+from .gated_units import ClampedGLU, RoutedExperts, SquaredRelu
+from .mlstm import MLstmMixer
+from .embedding import PairHashEmbedding
+from .block import Block, BranchNormBlock, ResidualStream
 
 __all__ = ["FeedForward", "KVNeed", "Mixer", "Norm", "RMSNorm", "Part", "StateNeed", "TensorSpec", "RotaryTable",
            "AttentionMixer", "ShortConvMixer", "SwiGLU", "Block", "ResidualStream", "LayerNorm", "ScaledRotaryTable",
-           "LatentAttentionMixer", "Mamba2Mixer", "ClampedGLU", "RoutedExperts"]
+           "LatentAttentionMixer", "Mamba2Mixer", "ClampedGLU", "RoutedExperts", "SquaredRelu", "MLstmMixer",
+           "PairHashEmbedding", "BranchNormBlock"]

@@ -6,6 +6,15 @@ One matrix product gives q, k, v and the gate logits: the four weights are stack
 load ([q; k; v; gate], the gate rows padded to a multiple of 8). The cache keeps normed,
 rotated keys and raw values. A call that reads another call's cache computes q (and the
 gate) only.
+
+Masks: every earlier key; a sliding window (`window`); or the query's own block of `chunk`
+positions, counted from the sequence's first position (the kernels take one number: 0, W or -C).
+
+Value heads of another size than the key heads (`v_dim`, without rotation): the kernels and
+the cache know one head size, so q, k and v heads are laid out in `padded_head_dim(spec)`
+channels, the surplus rows of their weights (and columns of the output projection) being
+zero: scores and outputs do not change. The per-head norms then see a mean over more
+channels; their eps and weights are scaled so that the result is the norm over head_dim.
 """
 from __future__ import annotations
 
@@ -34,6 +43,31 @@ def decode_splits(tiles: int, blocks: int, slots: int, fixed: float = 2.0) -> in
     return best
 
 
+_TENSOR_CORE_HEAD_DIMS = (16, 32, 48, 64, 96, 128)
+
+
+def padded_head_dim(spec) -> int:
+    """The one head size in which a layer's q, k and v heads are laid out: head_dim, unless the value heads differ (or it is odd);
+    then the next size the tensor-core kernels take, or the next even number above 128."""
+    vd = spec.v_dim or spec.head_dim
+    if vd == spec.head_dim and vd % 2 == 0:
+        return spec.head_dim
+    m = max(vd, spec.head_dim)
+    for d in _TENSOR_CORE_HEAD_DIMS:
+        if m <= d:
+            return d
+    return m + (m & 1)
+
+
+def _pad_heads(t: torch.Tensor, heads: int, d: int, dp: int) -> torch.Tensor:
+    """[heads * d, ...] -> [heads * dp, ...]: every head's rows followed by dp - d zero rows."""
+    if d == dp:
+        return t
+    t = t.reshape(heads, d, *t.shape[1:])
+    pad = torch.zeros(heads, dp - d, *t.shape[2:], dtype=t.dtype)
+    return torch.cat([t, pad], 1).reshape(heads * dp, *t.shape[2:])
+
+
 class AttentionMixer(Mixer):
     kind = "attention"
     fuses_norm = True
@@ -42,39 +76,53 @@ class AttentionMixer(Mixer):
     @classmethod
     def tensors(cls, spec) -> Dict[str, TensorSpec]:
         n = spec.names
+        vd = spec.v_dim or spec.head_dim
         qd, kd = spec.heads * spec.head_dim, spec.kv_heads * spec.head_dim
-        out = {
-            n["q"]: TensorSpec((qd, spec.hidden)), n["k"]: TensorSpec((kd, spec.hidden)),
-            n["v"]: TensorSpec((kd, spec.hidden)), n["o"]: TensorSpec((spec.hidden, qd)),
-        }
+        out = {n["q"]: TensorSpec((qd, spec.hidden))}
+        if spec.own_kv:
+            out[n["k"]] = TensorSpec((kd, spec.hidden))
+            out[n["v"]] = TensorSpec((spec.kv_heads * vd, spec.hidden))
+        out[n["o"]] = TensorSpec((spec.hidden, spec.heads * vd))
         if spec.head_gate:
             out[n["gate"]] = TensorSpec((spec.heads, spec.hidden))
         if spec.qk_norm:
             out[n["q_norm"]] = TensorSpec((spec.head_dim,), init="ones", role="vector")
-            out[n["k_norm"]] = TensorSpec((spec.head_dim,), init="ones", role="vector")
+            if spec.own_kv:
+                out[n["k_norm"]] = TensorSpec((spec.head_dim,), init="ones", role="vector")
         if spec.qkv_bias:
             out[n["q_bias"]] = TensorSpec((qd,), init="zeros", role="vector")
-            out[n["k_bias"]] = TensorSpec((kd,), init="zeros", role="vector")
-            out[n["v_bias"]] = TensorSpec((kd,), init="zeros", role="vector")
+            if spec.own_kv:
+                out[n["k_bias"]] = TensorSpec((kd,), init="zeros", role="vector")
+                out[n["v_bias"]] = TensorSpec((spec.kv_heads * vd,), init="zeros", role="vector")
         return out
 
     @classmethod
     def cache_need(cls, spec):
-        return KVNeed(spec.kv_heads, spec.head_dim, spec.window)
+        # (a block mask keeps every key: a reader of this cache may have another mask)
+        return KVNeed(spec.kv_heads, padded_head_dim(spec), spec.window if not spec.chunk else 0)
 
     def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
-        if spec.head_dim % 2 != 0 or spec.head_dim > 256:
-            raise ValueError(f"attention: head_dim {spec.head_dim} must be even and at most 256")
+        vd = spec.v_dim or spec.head_dim
+        D = self.D = padded_head_dim(spec)
+        if D % 2 != 0 or D > 256:
+            raise ValueError(f"attention: head sizes {spec.head_dim} / {vd} must be even (or differ) and at most 256")
         if spec.heads % spec.kv_heads != 0:
             raise ValueError(f"attention: {spec.heads} heads over {spec.kv_heads} kv heads")
+        if spec.chunk and spec.window:
+            raise ValueError("attention: a layer has a window or a block mask, not both")
+        if D != spec.head_dim and spec.position is not None:
+            raise ValueError("attention: value heads of another size than the key heads need a layer without rotation")
         self.spec, self.rt = spec, rt
+        self.mask = -int(spec.chunk) if spec.chunk else int(spec.window)     # the kernels' one number
         n = spec.names
-        self.q_dim = spec.heads * spec.head_dim
-        self.kv_dim = spec.kv_heads * spec.head_dim
+        self.q_dim = spec.heads * D
+        self.kv_dim = spec.kv_heads * D
+        # the per-head norm over head_dim channels, computed over D: sum / D + eps' = (head_dim / D) (sum / head_dim + eps)
+        self.qk_eps = float(spec.qk_norm_eps) * spec.head_dim / D
+        norm_scale = (spec.head_dim / D) ** 0.5
         # A checkpoint whose rotation couples channels 2i and 2i + 1 is brought into the rotate-half order here: within
         # every head the even channels first, then the odd ones, for q and k alike (their products do not change), and
         # the per-head norm weights with them.
-        D = spec.head_dim
         interleaved = spec.position is not None and getattr(spec.position, "pairing", "half") == "interleaved"
         order = torch.cat([torch.arange(0, D, 2), torch.arange(1, D, 2)]) if interleaved else None
 
@@ -83,14 +131,21 @@ class AttentionMixer(Mixer):
                 return t
             return t.reshape(heads, D, *t.shape[1:])[:, order].reshape(t.shape)
 
-        wq, wk = per_head(weights[n["q"]], spec.heads), per_head(weights[n["k"]], spec.kv_heads)
-        rows = [wq, wk, weights[n["v"]]]
+        hd = spec.head_dim
+        wq = _pad_heads(per_head(weights[n["q"]], spec.heads), spec.heads, hd, D)
         q_rows = [wq]
+        rows = [wq]
+        if spec.own_kv:
+            rows += [_pad_heads(per_head(weights[n["k"]], spec.kv_heads), spec.kv_heads, hd, D),
+                     _pad_heads(weights[n["v"]], spec.kv_heads, vd, D)]
         biases = q_biases = None
         if spec.qkv_bias:
-            bq = per_head(weights[n["q_bias"]], spec.heads)
-            biases = [bq, per_head(weights[n["k_bias"]], spec.kv_heads), weights[n["v_bias"]]]
+            bq = _pad_heads(per_head(weights[n["q_bias"]], spec.heads), spec.heads, hd, D)
             q_biases = [bq]
+            biases = [bq]
+            if spec.own_kv:
+                biases += [_pad_heads(per_head(weights[n["k_bias"]], spec.kv_heads), spec.kv_heads, hd, D),
+                           _pad_heads(weights[n["v_bias"]], spec.kv_heads, vd, D)]
         if spec.head_gate:
             g = weights[n["gate"]]
             pad = (-g.shape[0]) % 16      # (whole 16-row tiles: what the few-row product's unpredicated instances and its tails ask for)
@@ -101,25 +156,36 @@ class AttentionMixer(Mixer):
             if biases is not None:
                 biases.append(torch.zeros(g.shape[0]))
                 q_biases.append(torch.zeros(g.shape[0]))
-        self.w_qkvg = rt.matrix(torch.cat([r.to(torch.float32) for r in rows], 0))
-        self.b_qkvg = rt.vector(torch.cat([b.to(torch.float32) for b in biases])) if biases is not None else None
+        self.w_qkvg = self.b_qkvg = self.w_qg = self.b_qg = None
+        if spec.own_kv:
+            self.w_qkvg = rt.matrix(torch.cat([r.to(torch.float32) for r in rows], 0))
+            self.b_qkvg = rt.vector(torch.cat([b.to(torch.float32) for b in biases])) if biases is not None else None
         self._q_rows, self._q_biases = q_rows, q_biases          # stacked on the device on the first use as a reader of another cache
-        self.w_qg = self.b_qg = None
-        self.w_o = rt.matrix(weights[n["o"]])
-        self.q_norm = rt.vector(per_head(weights[n["q_norm"]], 1)) if spec.qk_norm else None
-        self.k_norm = rt.vector(per_head(weights[n["k_norm"]], 1)) if spec.qk_norm else None
+        w_o = weights[n["o"]]
+        if D != vd:         # zero columns where the padded value channels stand
+            w_o = _pad_heads(w_o.t().contiguous(), spec.heads, vd, D).t().contiguous()
+        self.w_o = rt.matrix(w_o)
+
+        def norm_weight(name):
+            return rt.vector(_pad_heads(per_head(weights[name], 1).to(torch.float32), 1, hd, D) * norm_scale)
+
+        self.q_norm = norm_weight(n["q_norm"]) if spec.qk_norm else None
+        self.k_norm = norm_weight(n["k_norm"]) if spec.qk_norm and spec.own_kv else None
         self.position = (registry.position_class(spec.position.kind)(spec.position, rt)
                          if spec.position is not None else None)
 
     def takes_prenormed(self, rows: int) -> bool:
-        return self.rt.few_rows_shape(rows, self.w_qkvg) and self.w_qkvg.shape[1] % 8 == 0
+        return (self.w_qkvg is not None and self.rt.few_rows_shape(rows, self.w_qkvg) and self.w_qkvg.shape[1] % 8 == 0)
 
     def forward(self, x, step, cache, into=None) -> torch.Tensor:
         s, rt = self.spec, self.rt
         T = x.shape[0]
         if cache is None or cache.storage is None:
             raise RuntimeError("attention needs a key/value cache")
+        D = self.D
         if cache.owner:
+            if self.w_qkvg is None:
+                raise RuntimeError("attention: a layer without keys and values of its own must read another call's cache")
             w_in, b_in, gate_at = self.w_qkvg, self.b_qkvg, self.q_dim + 2 * self.kv_dim
         else:
             if self.w_qg is None:
@@ -129,20 +195,20 @@ class AttentionMixer(Mixer):
             w_in, b_in, gate_at = self.w_qg, self.b_qg, self.q_dim
         table = step.page_tables[cache.group]
         rope = self.position.table(step.max_positions) if self.position is not None else None
-        q = rt.ws.get("attn_q", (T, s.heads, s.head_dim), rt.act_dtype)
-        if step.decode and rt.rope_behind_product(x, w_in, s.head_dim):
+        q = rt.ws.get("attn_q", (T, s.heads, D), rt.act_dtype)
+        if step.decode and rt.rope_behind_product(x, w_in, D):
             # one token a sequence: the per-head norms, the rotation and the cache write run behind the product, in its kernel
             proj = rt.ws.get("attn_qkv", (T, w_in.shape[0]), rt.act_dtype)
             rt.few_rows_rope(x, w_in, proj, b_in, q_out=q, pool=cache.storage if cache.owner else None,
                              page_table=table if cache.owner else None, seq_of_token=step.seq_of_token,
                              positions=step.positions, q_w=self.q_norm, k_w=self.k_norm, rope=rope, heads=s.heads,
-                             kv_heads=s.kv_heads, head_dim=s.head_dim, page_size=step.page_size, eps=s.qk_norm_eps)
+                             kv_heads=s.kv_heads, head_dim=D, page_size=step.page_size, eps=self.qk_eps)
         else:
             proj = rt.linear(x, w_in, "attn_qkv", b_in)
             ops.qk_norm_rope_store(proj, q, cache.storage, table, step.seq_of_token, step.positions, self.q_norm,
-                                   self.k_norm, rope, s.heads, s.kv_heads, s.head_dim, step.page_size, s.qk_norm_eps,
+                                   self.k_norm, rope, s.heads, s.kv_heads, D, step.page_size, self.qk_eps,
                                    write_kv=cache.owner)
-        o = rt.ws.get("attn_o", (T, s.heads, s.head_dim), rt.act_dtype)
+        o = rt.ws.get("attn_o", (T, s.heads, D), rt.act_dtype)
         gate = proj[:, gate_at:] if s.head_gate else None
         self.attend(q, cache, table, step, gate, o)
         if into is not None:
@@ -150,47 +216,47 @@ class AttentionMixer(Mixer):
         return rt.linear(o.view(T, self.q_dim), self.w_o, "mixer_out")
 
     def attend(self, q, cache, table, step, gate, o) -> None:
-        s, rt = self.spec, self.rt
-        if step.fixed_shape and rt.mode == "bfloat16" and ops.attention_mma_supports(s.head_dim, step.page_size, s.heads // s.kv_heads):
+        s, rt, D, mask = self.spec, self.rt, self.D, self.mask
+        if step.fixed_shape and rt.mode == "bfloat16" and ops.attention_mma_supports(D, step.page_size, s.heads // s.kv_heads):
             # a step captured for any lengths up to its bounds: one key split, grids from the bounds
-            if rt.prompt_attention == "tcgen05" and ops.attention_tc_supports(s.head_dim, step.page_size, s.heads // s.kv_heads):
+            if rt.prompt_attention == "tcgen05" and ops.attention_tc_supports(D, step.page_size, s.heads // s.kv_heads):
                 ops.attention_tc(q, cache.storage, table, step.cu_seqlens, step.kv_lens, gate, o, step.n_seqs,
-                                 step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window, step.max_kv_len)
+                                 step.max_q_len, s.kv_heads, step.page_size, s.scale, mask, step.max_kv_len)
             else:
                 ops.attention_mma(q, cache.storage, table, step.cu_seqlens, step.kv_lens, gate, o, None, step.n_seqs,
-                                  step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window, 1)
+                                  step.max_q_len, s.kv_heads, step.page_size, s.scale, mask, 1)
             return
-        if rt.mode == "bfloat16" and ops.attention_mma_supports(s.head_dim, step.page_size, s.heads // s.kv_heads):
+        if rt.mode == "bfloat16" and ops.attention_mma_supports(D, step.page_size, s.heads // s.kv_heads):
             # Few tiles and long key ranges (decoding): split each range over several CTAs so that
             # every SM streams a part of the cache; the partial results meet in scratch memory.
             tokens_per_tile = 64 // (s.heads // s.kv_heads)
             tiles = sum(-(-int(n) // tokens_per_tile) for n in step.q_lens_host) * s.kv_heads
             blocks = -(-step.max_kv_len // step.page_size)
-            if s.window > 0:
-                blocks = min(blocks, -(-(s.window + step.max_q_len) // step.page_size) + 1)
+            if s.window > 0 or s.chunk > 0:       # the keys a tile can see span at most so many pages
+                blocks = min(blocks, -(-(max(s.window, s.chunk) + step.max_q_len) // step.page_size) + 1)
             if step.decode and s.heads // s.kv_heads <= 16 and rt.attn_split_factor == 0:
-                splits = decode_splits(tiles, blocks, max(1, ops.attention_mma_decode_slots(s.head_dim, tiles)),
+                splits = decode_splits(tiles, blocks, max(1, ops.attention_mma_decode_slots(D, tiles)),
                                        rt.attn_fixed_cost)
             else:
                 splits = max(1, min(blocks, 32, (max(rt.attn_split_factor, 1) * rt.sm_count) // max(tiles, 1)))
             # prompts: the tcgen05 kernel, unless few tiles face many keys (a short piece of a long sequence), where
             # cutting the keys over more CTAs is worth more
             if ((splits == 1 or step.max_kv_len <= 512) and not step.decode and rt.prompt_attention == "tcgen05"
-                    and ops.attention_tc_supports(s.head_dim, step.page_size, s.heads // s.kv_heads)):
+                    and ops.attention_tc_supports(D, step.page_size, s.heads // s.kv_heads)):
                 ops.attention_tc(q, cache.storage, table, step.cu_seqlens, step.kv_lens, gate, o, step.n_seqs,
-                                 step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window, step.max_kv_len)
+                                 step.max_q_len, s.kv_heads, step.page_size, s.scale, mask, step.max_kv_len)
                 return
             scratch = None
             if splits > 1:
-                need = ops.attention_mma_scratch_bytes(q.shape[0] * s.heads, s.head_dim, splits)
+                need = ops.attention_mma_scratch_bytes(q.shape[0] * s.heads, D, splits)
                 scratch = rt.ws.get("attn_scratch", (need,), torch.uint8)
             counters = rt.attn_counters if (rt.fuse_tails and rt.tail_attn and step.n_seqs * s.kv_heads <= rt.attn_counters.numel()) else None
             ops.attention_mma(q, cache.storage, table, step.cu_seqlens, step.kv_lens, gate, o, scratch, step.n_seqs,
-                              step.max_q_len, s.kv_heads, step.page_size, s.scale, s.window, splits, counters=counters,
+                              step.max_q_len, s.kv_heads, step.page_size, s.scale, mask, splits, counters=counters,
                               bounded_waits=step.decode)
             return
         ops.attention_generic(q, cache.storage, table, step.seq_of_token, step.positions, gate, o, s.kv_heads,
-                              step.page_size, s.scale, s.window)
+                              step.page_size, s.scale, mask)
 
 
 registry.register_mixer(AttentionMixer.kind, AttentionMixer)

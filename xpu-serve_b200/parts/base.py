@@ -63,7 +63,7 @@ class KVNeed:
 class StateNeed:
     """A fixed-size state per sequence, zero at a sequence's start."""
     shape: Tuple[int, ...]
-    dtype: str = "compute"   # "compute": the activation dtype; "float32"
+    dtype: str = "compute"   # "compute": the activation dtype; "float32"; "int32"
 
 
 class Part:
@@ -123,3 +123,10 @@ class Norm(Part):
             h.add_(post.normed(branch).float() if post is not None else branch.float())
         if y is not None:
             y.copy_(self.normed(h if rows is None else h.index_select(0, rows.long())))
+
+    def add_copy(self, h, branch, post: Optional["Norm"], y) -> None:
+        """h += post(branch) (branch alone without `post`; nothing without a branch); then y = h in y's element type:
+        what a layer wants whose sublayers read the stream itself."""
+        if branch is not None:
+            h.add_(post.normed(branch).float() if post is not None else branch.float())
+        y.copy_(h)

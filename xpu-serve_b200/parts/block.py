@@ -114,6 +114,18 @@ class ResidualStream:
             return Prenormed(self._pre[1], self._pre[2], self.h.shape[1], norm.eps)
         return self.norm(norm)
 
+    def plain(self, norm: Norm) -> torch.Tensor:
+        """The stream itself in the activation type, after any pending branch joined it: what a sublayer reads in a
+        layer without norms before its sublayers. `norm`: any norm of the model (its `add_copy` does the work)."""
+        self._flip ^= 1
+        y = self.rt.ws.get(f"normed{self._flip}", tuple(self.h.shape), self.rt.act_dtype)
+        m, post = self._pending if self._pending is not None else (None, None)
+        norm.add_copy(self.h, m, post, y)
+        self._pending = None
+        self._pre = None
+        self._plain_add = norm
+        return y
+
     def norm(self, norm: Norm, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         """`norm` of the stream (after any pending branch joined it), in the activation type.
         With `rows`, only those rows, packed."""
@@ -193,4 +205,44 @@ class Block:
             stream.add(self.ffn.forward(y, step), self.post_ffn)
 
 
+class BranchNormBlock:
+    """h += norm1(mixer(h)); h += norm2(ffn(h)): the sublayers read the stream itself (in the activation type), and
+    the layer's two norms act on what they return. The sum with the normed branch and the copy that the next sublayer
+    reads are one kernel (`ResidualStream.plain`)."""
+    kind = "branch_norm"
+    fixed_shape_ok = True
+
+    @classmethod
+    def tensors(cls, layer) -> Dict[str, TensorSpec]:
+        out: Dict[str, TensorSpec] = {}
+        norm_cls = registry.norm_class(layer.norm.kind)
+        for key in ["post_mixer"] + (["post_ffn"] if layer.ffn is not None else []):
+            out.update(norm_cls.tensors(layer.norm, layer.names[key]))
+        out.update(registry.mixer_class(layer.mixer.kind).tensors(layer.mixer))
+        if layer.ffn is not None:
+            out.update(registry.ffn_class(layer.ffn.kind).tensors(layer.ffn))
+        return out
+
+    @classmethod
+    def cache_need(cls, layer):
+        return registry.mixer_class(layer.mixer.kind).cache_need(layer.mixer)
+
+    def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
+        self.spec, self.rt = spec, rt
+        self.mixer = registry.mixer_class(spec.mixer.kind)(spec.mixer, weights, rt)
+        self.ffn = registry.ffn_class(spec.ffn.kind)(spec.ffn, weights, rt) if spec.ffn is not None else None
+        norm_cls = registry.norm_class(spec.norm.kind)
+        self.post_mixer = norm_cls(spec.norm, weights, spec.names["post_mixer"], rt)
+        self.post_ffn = norm_cls(spec.norm, weights, spec.names["post_ffn"], rt) if self.ffn is not None else None
+        self.first_norm = None                # no norm reads the stream for this block: nothing to prepare for it
+
+    def forward(self, stream: ResidualStream, step, cache, next_norm: Optional[Norm] = None) -> None:
+        x = stream.plain(self.post_mixer)
+        stream.add(self.mixer.forward(x, step, cache), self.post_mixer)
+        if self.ffn is not None:
+            y = stream.plain(self.post_ffn)
+            stream.add(self.ffn.forward(y, step), self.post_ffn)
+
+
 registry.register_arrangement(Block.kind, Block)
+registry.register_arrangement(BranchNormBlock.kind, BranchNormBlock)

@@ -1,10 +1,14 @@
-"""Two more feed-forwards: a clamped gated unit, and routed experts.
+"""More feed-forwards: a clamped gated unit, a squared-ReLU unit, and routed experts.
 
 ClampedGLU:     down(g * sigmoid(alpha g) * (u + up_shift)), g = min(gate x, limit), u = clamp(up x, -limit, limit).
-RoutedExperts:  `experts` SwiGLU feed-forwards without biases; a token's router logits (float32) choose the `top`
-                largest, whose softmax over themselves weights the chosen experts' outputs. On the device the step's
+SquaredRelu:    down(max(up x, 0)^2).
+RoutedExperts:  `experts` gated feed-forwards without biases (SwiGLU, or clamped units when the spec gives a limit); a
+                token's router logits (float32) choose the `top` largest, whose softmax over themselves, times the
+                spec's `route_scale`, weights the chosen experts' outputs. On the device the step's
                 (token, choice) rows are sorted by expert and the two products walk row tiles of one expert each
                 (csrc/experts.cu); no count ever reaches the host, so a step with experts can be captured in a graph.
+                With `shared`, a clamped unit that every token uses joins the sum, times the sigmoid of one more
+                logit a token (its one-row matrix is the router's last row here, so the router product gives both).
 """
 from __future__ import annotations
 
@@ -44,7 +48,8 @@ class ClampedGLU(FeedForward):
         self.w_gate_up = rt.matrix(stacked)
         self.w_down = rt.matrix(weights[n["down"]])
 
-    def forward(self, y, step) -> torch.Tensor:
+    def forward(self, y, step, name: str = "ffn_out") -> torch.Tensor:
+        """`name`: the scratch buffer that takes the result (a unit inside another feed-forward names its own)."""
         rt, s = self.rt, self.spec
         act = rt.ws.get("ffn_act", (y.shape[0], s.intermediate), rt.act_dtype)
         if self.interleave and rt.tensor_core_product(y, self.w_gate_up, fused=True):
@@ -52,6 +57,28 @@ class ClampedGLU(FeedForward):
         else:
             gu = rt.linear(y, self.w_gate_up, "ffn_gate_up")
             ops.clamped_glu(gu, act, s.limit, s.alpha, s.up_shift, self.interleave)
+        return rt.linear(act, self.w_down, name)
+
+
+class SquaredRelu(FeedForward):
+    kind = "squared_relu"
+    fixed_shape_ok = True
+
+    @classmethod
+    def tensors(cls, spec) -> Dict[str, TensorSpec]:
+        n = spec.names
+        return {n["up"]: TensorSpec((spec.intermediate, spec.hidden)), n["down"]: TensorSpec((spec.hidden, spec.intermediate))}
+
+    def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
+        self.spec, self.rt = spec, rt
+        self.w_up = rt.matrix(weights[spec.names["up"]])
+        self.w_down = rt.matrix(weights[spec.names["down"]])
+
+    def forward(self, y, step) -> torch.Tensor:
+        rt = self.rt
+        up = rt.linear(y, self.w_up, "ffn_up")
+        act = rt.ws.get("ffn_act", (y.shape[0], self.spec.intermediate), rt.act_dtype)
+        ops.relu_squared(up, act)
         return rt.linear(act, self.w_down, "ffn_out")
 
 
@@ -68,6 +95,9 @@ class RoutedExperts(FeedForward):
             out[n["up"].format(e=e)] = TensorSpec((spec.intermediate, spec.hidden))
             out[n["down"].format(e=e)] = TensorSpec((spec.hidden, spec.intermediate))
         out[n["router"]] = TensorSpec((spec.experts, spec.hidden))
+        if spec.shared is not None:
+            out.update(ClampedGLU.tensors(spec.shared))
+            out[n["shared_gate"]] = TensorSpec((1, spec.hidden))
         return out
 
     def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
@@ -90,20 +120,29 @@ class RoutedExperts(FeedForward):
 
         self.w_gate_up = rt.matrix(torch.stack([stacked(e) for e in range(spec.experts)]))
         self.w_down = rt.matrix(torch.stack([weights[n["down"].format(e=e)].to(torch.float32) for e in range(spec.experts)]))
-        self.w_router = rt.matrix(weights[n["router"]])
+        router = weights[n["router"]].to(torch.float32)
+        self.shared = None
+        if spec.shared is not None:
+            # the shared unit's gate logit is one more row of the router product (its float32 sums serve both)
+            router = torch.cat([router, weights[n["shared_gate"]].to(torch.float32).reshape(1, H)], 0)
+            self.shared = ClampedGLU(spec.shared, weights, rt)
+        self.w_router = rt.matrix(router)
+        self.clamp = (spec.limit, spec.alpha, spec.up_shift) if spec.limit > 0 else None
 
     def forward(self, y, step) -> torch.Tensor:
         rt, s = self.rt, self.spec
         T, n = y.shape[0], y.shape[0] * s.top
         ws = rt.ws
-        logits = ws.get("moe_logits", (T, s.experts), torch.float32)
+        shared = self.shared.forward(y, step, name="moe_shared") if self.shared is not None else None
+        logits = ws.get("moe_logits", (T, self.w_router.shape[0]), torch.float32)
         ops.moe_logits(y, self.w_router, logits)            # float32 sums of the activation type's products, not rounded
+        shared_gate = logits[:, s.experts:] if shared is not None else None
         ids = ws.get("moe_ids", (n,), torch.int32)
         wts = ws.get("moe_wts", (n,), torch.float32)
         place = ws.get("moe_place", (n,), torch.int32)
         source = ws.get("moe_source", (n,), torch.int32)
         meta = ws.get("moe_meta", (4 + 3 * ops.moe_max_tiles(n, s.experts),), torch.int32)
-        ops.moe_route(logits, s.top, ids, wts)
+        ops.moe_route(logits, s.top, ids, wts, experts=s.experts, scale=s.route_scale)
         out = ws.get("ffn_out", (T, s.hidden), rt.act_dtype)
         if self.tensor_cores:
             # every expert's rows padded to tiles of 128: gather, two tcgen05 products over the plan's tiles, combine
@@ -114,19 +153,20 @@ class RoutedExperts(FeedForward):
             rows_in = ws.get("moe_rows_in", (128 * tiles, s.hidden), rt.act_dtype)
             ops.moe_gather(y, source, s.top, rows_in)
             act = ws.get("moe_act", (128 * tiles, s.intermediate), rt.act_dtype)
-            ops.gemm_tc_grouped(rows_in, self.w_gate_up, act, meta, tiles, glu=True)
+            ops.gemm_tc_grouped(rows_in, self.w_gate_up, act, meta, tiles, glu=True, clamp=self.clamp)
             rows_out = ws.get("moe_rows", (128 * tiles, s.hidden), rt.act_dtype)
             ops.gemm_tc_grouped(act, self.w_down, rows_out, meta, tiles, glu=False)
-            ops.moe_combine(rows_out, place, wts, out, s.top)
+            ops.moe_combine(rows_out, place, wts, out, s.top, shared, shared_gate)
             return out
         ops.moe_plan(ids, s.experts, place, source, meta)
         act = ws.get("moe_act", (n, s.intermediate), rt.act_dtype)
-        ops.moe_gemm(y, self.w_gate_up, act, meta, n, source, s.top, glu=True)
+        ops.moe_gemm(y, self.w_gate_up, act, meta, n, source, s.top, glu=True, clamp=self.clamp)
         rows_out = ws.get("moe_rows", (n, s.hidden), rt.act_dtype)
         ops.moe_gemm(act, self.w_down, rows_out, meta, n, None, s.top, glu=False)
-        ops.moe_combine(rows_out, place, wts, out, s.top)
+        ops.moe_combine(rows_out, place, wts, out, s.top, shared, shared_gate)
         return out
 
 
 registry.register_ffn(ClampedGLU.kind, ClampedGLU)
+registry.register_ffn(SquaredRelu.kind, SquaredRelu)
 registry.register_ffn(RoutedExperts.kind, RoutedExperts)

@@ -36,4 +36,11 @@ class RMSNorm(Norm):
                         self.eps, self.eps if post is None else post.eps)
 
 
+    def add_copy(self, h, branch, post: Optional[Norm], y) -> None:
+        if post is not None and not isinstance(post, RMSNorm):
+            return super().add_copy(h, branch, post, y)
+        ops.add_rmsnorm(h, branch, None if post is None else post.w, None, y, None, self.eps,
+                        self.eps if post is None else post.eps)
+
+
 registry.register_norm(RMSNorm.kind, RMSNorm)

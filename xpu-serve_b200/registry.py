@@ -26,6 +26,7 @@ _FFNS: Dict[str, type] = {}
 _POSITIONS: Dict[str, type] = {}
 _NORMS: Dict[str, type] = {}
 _ARRANGEMENTS: Dict[str, type] = {}
+_EMBEDDINGS: Dict[str, type] = {}
 
 
 def register_architecture(name: str, config_class: type, aliases=()) -> None:
@@ -85,6 +86,15 @@ def register_norm(kind: str, cls: type) -> None:
 def register_arrangement(kind: str, cls: type) -> None:
     """How one layer's norms, mixer and feed-forward are wired (parts/block.py registers "pre_norm")."""
     _register(_ARRANGEMENTS, "layer arrangement", kind, cls)
+
+
+def register_embedding(kind: str, cls: type) -> None:
+    """How token ids become the stream's first rows, when it is more than a table lookup (parts/embedding.py)."""
+    _register(_EMBEDDINGS, "embedding", kind, cls)
+
+
+def embedding_class(kind: str) -> type:
+    return _lookup(_EMBEDDINGS, "embedding", kind)
 
 
 def mixer_class(kind: str) -> type:

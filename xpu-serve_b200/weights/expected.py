@@ -20,6 +20,9 @@ def expected_tensors(spec: ModelSpec, prefix: Optional[str] = None) -> Dict[str,
     p = spec.prefixes[-1] if prefix is None else prefix
     out: Dict[str, TensorSpec] = {}
     out[p + spec.names["embed"]] = TensorSpec((spec.vocab, spec.hidden))
+    if spec.embedding is not None:
+        for rel, ts in registry.embedding_class(spec.embedding.kind).tensors(spec.embedding).items():
+            out[p + rel] = ts
     for rel, ts in registry.norm_class(spec.final_norm.kind).tensors(spec.final_norm, spec.names["final_norm"]).items():
         out[p + rel] = ts
     if not spec.tied_head:
