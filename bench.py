@@ -121,6 +121,96 @@ def run_saralix_stacks(batch: int, steps: int, warmup: int, only=None) -> int:
     return 0
 
 
+# Nimelorn layer stacks (`--workload nimelorn`; random weights), each beside the closest existing stack of equal width, layer
+# count and vocabulary and about equal weights: block-masked attention beside LFM3's sliding-window attention (a squared-ReLU
+# unit of 8,192 holds what a SwiGLU of 5,504 holds), and the mLSTM recurrence beside Saralix's Mamba-2, both with routed experts.
+def _blocked(heads, kv_heads, dim, vdim, size):
+    return {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "mask": {"size": size}, "scale": dim ** -0.5}
+
+
+_N_MOE = {"kind": "moe", "expert": {"ff": 1024, "limit": 7.0}, "router": {"experts": 16, "top": 4, "scale": 1.0},
+          "shared": {"ff": 1024, "limit": 7.0}}
+NIMELORN_STACKS = {
+    # name: (Nimelorn layers, the stack beside it: ("lfm3", layer types, feed-forward width, window) or ("saralix", stack name))
+    "blocked_dense": ([("attention", _blocked(32, 8, 64, 64, 1024), {"kind": "dense", "ff": 8192})] * 2,
+                      ("lfm3", ["sliding_attention"] * 2, 5504, 1024)),
+    "wide_values_experts": ([("attention", _blocked(16, 4, 64, 96, 1024), _N_MOE)] * 2,
+                            ("lfm3", ["sliding_attention"] * 2, 5120, 1024)),
+    "mlstm_experts": ([("mlstm", {"heads": 16, "dim": 64, "vdim": 128, "gate_cap": 15.0}, _N_MOE)] * 2,
+                      ("saralix", "mamba2_experts")),
+}
+
+
+def nimelorn_stack_configs(name: str, width: int = 2048, vocab: int = 32768):
+    from xpu_serve_b200.config import Lfm3Config, NimelornConfig, SaralixConfig
+    layers, beside = NIMELORN_STACKS[name]
+    ours = {"architecture": "Nimelorn", "width": width, "vocab": vocab, "norm": {"eps": 1e-5},
+            "embedding": {"scale": float(width) ** 0.5, "bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 31}},
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in layers]}
+    if beside[0] == "saralix":
+        return NimelornConfig.from_json(ours), ("saralix", SaralixConfig.from_json(saralix_stack_configs(beside[1], width, vocab)[0]))
+    _, kinds, ffn, window = beside
+    other = dict(SHAPE_1_2B)
+    other.update(vocab_size=vocab, hidden_size=width, intermediate_size=ffn, num_hidden_layers=len(kinds), layer_types=kinds,
+                 max_position_embeddings=CONTEXT)
+    other.pop("rope_theta")
+    other["rope_parameters"] = {k: {"rope_theta": 1000000.0} for k in set(kinds) if k != "conv"}
+    if window:
+        other["sliding_window"] = window
+    return NimelornConfig.from_json(ours), ("lfm3", Lfm3Config.from_json(other))
+
+
+def run_nimelorn_stacks(batch: int, steps: int, warmup: int, only=None) -> int:
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 after 2,048-token prompts, CUDA graph) of
+    each Nimelorn stack and of the stack beside it, device-timed as the headline's points are. With XS_PROFILE=1 the
+    kernels' own times are printed after each model (ops.profile_report)."""
+    import torch
+    from xpu_serve_b200 import load_model
+    from xpu_serve_b200.ops import lib as ops
+    from xpu_serve_b200.weights import write_random_model
+    points = {}
+    for name in NIMELORN_STACKS:
+        if only and name not in only:
+            continue
+        ours, (beside_label, beside) = nimelorn_stack_configs(name)
+        points[name] = {}
+        for label, config in (("nimelorn", ours), (beside_label, beside)):
+            with tempfile.TemporaryDirectory() as root:
+                folder = write_random_model(os.path.join(root, label), config, seed=0, dtype="bfloat16", std=0.02)
+                model = load_model(folder, dtype="bfloat16")
+            V = config.model_spec().vocab
+            prefill_ms = time_prefill(model, V, warmup=max(3, warmup // 2), runs=7)
+            if ops.watched():
+                print(f"# {name} {label}: prefill of {PROMPT} tokens", file=sys.stderr)
+                ops.profile_report(file=sys.stderr)
+            ms, launches = time_decode(model, batch, steps, warmup, V)
+            if ops.watched():
+                print(f"# {name} {label}: decode at batch {batch}", file=sys.stderr)
+                ops.profile_report(file=sys.stderr)
+            points[name][label] = {"prefill_ms": round(prefill_ms, 3), "prefill_tok_s": round(PROMPT * 1000.0 / prefill_ms, 1),
+                                   "decode_ms_per_step": round(ms, 4), "decode_tok_s": round(batch * 1000.0 / ms, 1),
+                                   "launches_per_step": round(launches, 1),
+                                   "parameters_m": round(sum(int(np_prod(ts.shape)) for ts in expected(config).values()) / 1e6, 1)}
+            del model
+            torch.cuda.empty_cache()
+    print(json.dumps({"workload": "nimelorn", "metric": "prefill tok/s (2,048 tokens) and decode tok/s (batch %d) of two-layer stacks" % batch,
+                      "dtype": "bf16", "data": "synthetic token ids, random weights N(0, 0.02)", "steps": steps, "warmup": warmup,
+                      "width": 2048, "vocab": 32768, "points": points}))
+    return 0
+
+
+def np_prod(shape) -> int:
+    n = 1
+    for v in shape:
+        n *= int(v)
+    return n
+
+
+def expected(config):
+    from xpu_serve_b200.weights.expected import expected_tensors
+    return expected_tensors(config.model_spec())
+
+
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -436,8 +526,8 @@ def main() -> int:
                          "at long context), which the default run adds to `points`")
     ap.add_argument("--only", default=None, choices=["decode", "prefill", "sample"],
                     help="time one part only and print a short line (for profiler captures)")
-    ap.add_argument("--stacks", default=None, help="with --workload saralix: a comma list of the stacks to run (all)")
-    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + ["saralix"],
+    ap.add_argument("--stacks", default=None, help="with --workload saralix or nimelorn: a comma list of the stacks to run (all)")
+    ap.add_argument("--workload", default=None, choices=sorted(WORKLOADS) + ["saralix", "nimelorn"],
                     help="instead of the default run: a batch of unequal prompts at another shape of the family")
     args = ap.parse_args()
 
@@ -453,6 +543,8 @@ def main() -> int:
     args.warmup = max(args.warmup, 3)
     if args.workload == "saralix":
         return run_saralix_stacks(args.batch or 8, args.steps or 128, args.warmup, args.stacks.split(",") if args.stacks else None)
+    if args.workload == "nimelorn":
+        return run_nimelorn_stacks(args.batch or 8, args.steps or 128, args.warmup, args.stacks.split(",") if args.stacks else None)
     if args.workload is not None:
         return run_workload(args.workload, args.layers, args.batch, args.steps)
     args.batch = args.batch or 8
