@@ -180,6 +180,23 @@ def test_long_prompts(dtype, replayers, folders):
     check("C", dtype, tu.batch_trace(reqs, 3, prompt_frac=0.985), reqs, replayers, folders, max_tokens=1280)
 
 
+def test_every_product_on_the_tcgen05_kernel(folders, monkeypatch):
+    """With the tcgen05 product forced for every number of rows, the squared ReLU runs in the up product's epilogue (C has
+    widths in blocks of 8); whole prompts and single tokens against the oracle."""
+    from xpu_serve_b200.engine.model import load_model
+    from xpu_serve_b200.engine.replay import Replayer
+    from xpu_serve_b200.ops import lib as ops
+    monkeypatch.setenv("XS_MANY_ROWS_GEMM", "tcgen05")
+    rp = Replayer(load_model(folders("C", "bfloat16"), dtype="bfloat16"), 1024, None)
+    assert rp.model.rt.many_rows == "tcgen05"
+    seen = []
+    real = ops.gemm_tc
+    monkeypatch.setattr(ops, "gemm_tc", lambda *a, **k: (seen.append((a[0].shape[0], k.get("epilogue"))), real(*a, **k))[1])
+    reqs = requests_for("C", [70, 131, 9])
+    check("C", "bfloat16", tu.tail_trace(reqs, tail=6), reqs, None, folders, replayer=rp)
+    assert (125, ops.EPI_RELU_SQ) in seen and (1, ops.EPI_RELU_SQ) in seen       # a whole prompt's rows, and a single token's
+
+
 def test_the_program_replays_a_trace(folders, tmp_path):
     """bin/trace_run over its standard input, in float32, against the oracle."""
     reqs = requests_for("C", [5, 40, 70])

@@ -149,6 +149,7 @@ __global__ void __launch_bounds__(NTHREADS, (D <= 64 ? 4 : 2)) attention_mma_ker
     const int r1 = warp * 16 + (lane >> 2), r2 = r1 + 8;
     const int pos1 = r1 < rows_valid ? pos0 + r1 / G : -1;
     const int pos2 = r2 < rows_valid ? pos0 + r2 / G : -1;
+    const int lo1 = xs_first_visible(pos1, p.window), lo2 = xs_first_visible(pos2, p.window);     // found once: may cost a division
 
     float o[DTILES][4];
 #pragma unroll
@@ -209,8 +210,8 @@ __global__ void __launch_bounds__(NTHREADS, (D <= 64 ? 4 : 2)) attention_mma_ker
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const int key = key0 + i * 8 + e;
-                        const bool v1 = xs_visible(pos1, key, p.window);
-                        const bool v2 = xs_visible(pos2, key, p.window);
+                        const bool v1 = key <= pos1 && key >= lo1;
+                        const bool v2 = key <= pos2 && key >= lo2;
                         s[i][e] = v1 ? s[i][e] * p.scale_log2 : -INFINITY;
                         s[i][2 + e] = v2 ? s[i][2 + e] * p.scale_log2 : -INFINITY;
                         mx1 = fmaxf(mx1, s[i][e]);
@@ -392,6 +393,7 @@ __global__ void __launch_bounds__(NTHREADS) attention_decode_mma_kernel(const At
     const int r1 = lane >> 2, r2 = r1 + 8;
     const int pos1 = r1 < rows_valid ? pos0 + r1 / G : -1;
     const int pos2 = r2 < rows_valid ? pos0 + r2 / G : -1;
+    const int lo1 = xs_first_visible(pos1, p.window), lo2 = xs_first_visible(pos2, p.window);     // found once: may cost a division
     float o[DTILES][4];
 #pragma unroll
     for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
@@ -437,8 +439,8 @@ __global__ void __launch_bounds__(NTHREADS) attention_decode_mma_kernel(const At
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int key = key0 + i * 8 + e;
-                const bool v1 = xs_visible(pos1, key, p.window);
-                const bool v2 = xs_visible(pos2, key, p.window);
+                const bool v1 = key <= pos1 && key >= lo1;
+                const bool v2 = key <= pos2 && key >= lo2;
                 s[i][e] = v1 ? s[i][e] * p.scale_log2 : -INFINITY;
                 s[i][2 + e] = v2 ? s[i][2 + e] * p.scale_log2 : -INFINITY;
                 mx1 = fmaxf(mx1, s[i][e]);
@@ -694,6 +696,7 @@ __global__ void __launch_bounds__(160) attention_decode_tma_kernel(const __grid_
     const int r1 = lane >> 2, r2 = r1 + 8;
     const int pos1 = r1 < rows_valid ? pos0 + r1 / G : -1;
     const int pos2 = r2 < rows_valid ? pos0 + r2 / G : -1;
+    const int lo1 = xs_first_visible(pos1, p.window), lo2 = xs_first_visible(pos2, p.window);     // found once: may cost a division
     float o[DTILES][4];
 #pragma unroll
     for (int i = 0; i < DTILES; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
@@ -737,8 +740,8 @@ __global__ void __launch_bounds__(160) attention_decode_tma_kernel(const __grid_
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int key = key0 + i * 8 + e;
-                const bool v1 = xs_visible(pos1, key, p.window);
-                const bool v2 = xs_visible(pos2, key, p.window);
+                const bool v1 = key <= pos1 && key >= lo1;
+                const bool v2 = key <= pos2 && key >= lo2;
                 sc[i][e] = v1 ? sc[i][e] * p.scale_log2 : -INFINITY;
                 sc[i][2 + e] = v2 ? sc[i][2 + e] * p.scale_log2 : -INFINITY;
                 mx1 = fmaxf(mx1, sc[i][e]);

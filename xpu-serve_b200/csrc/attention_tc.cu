@@ -298,6 +298,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
         const uint32_t s_col = (uint32_t)(grp * TN), o_col = kColO + (uint32_t)(grp * D);
         const int pos = r < rows_valid ? pos0 + r / G : -1;       // -1: the row sees nothing
+        const int lo_row = xs_first_visible(pos, p.window);         // the first key this row sees (found once: it may cost a division)
         float m = -INFINITY, l = 0.0f;
         bool bad = false;                                         // a wait gave up: nothing more is waited for
         int done = 0;                                             // blocks this group has finished
@@ -320,7 +321,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap tmap_kv, const AttnTcPar
 #pragma unroll
                 for (int e = 0; e < TN; ++e) {
                     const int key = key0 + e;
-                    const bool see = xs_visible(pos, key, p.window);   // pos -1: nothing
+                    const bool see = key <= pos && key >= lo_row;      // pos -1: nothing
                     if (!see) raw[e] = 0xff800000u;                // -inf: its weight will be exactly 0
                     mx4[e & 3] = fmaxf(mx4[e & 3], __uint_as_float(raw[e]));
                 }

@@ -36,7 +36,7 @@ constexpr int BM = 128;          // weight rows per tile (MMA M)
 constexpr int BK = 64;           // k per stage: one 128-byte swizzle atom of bfloat16
 constexpr int kThreads = 192;    // producer warp, MMA warp, four epilogue warps
 
-enum Epilogue : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2 };
+enum Epilogue : int { EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_SWIGLU = 2, EPI_RELU_SQ = 3 };     // 3: store max(v, 0)^2
 
 struct GemmTcParams {
     void* out;                // EPI_STORE: [T, N]; EPI_RESIDUAL: float [T, N]; EPI_SWIGLU: [T, N / 2]
@@ -85,6 +85,10 @@ __device__ __forceinline__ void emit(const GemmTcParams& p, float v, int row, in
         return;
     }
     if (row >= p.N || token >= p.T) return;
+    if (p.epilogue == EPI_RELU_SQ) {
+        v = fmaxf(v, 0.0f);
+        v *= v;
+    }
     const int64_t at = (int64_t)token * p.ldo + row;
     if (p.epilogue == EPI_RESIDUAL) ((float*)p.out)[at] += v;
     else if (p.out_f32) ((float*)p.out)[at] = v;
@@ -104,6 +108,13 @@ __device__ __forceinline__ void emit16(const GemmTcParams& p, const uint32_t* r,
 #pragma unroll
         for (int j = 0; j < 16; ++j)
             if (full || f0 + j < p.N) v[j] += __ldg(p.bias + f0 + j);
+    }
+    if (p.epilogue == EPI_RELU_SQ) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+            v[j] = fmaxf(v[j], 0.0f);
+            v[j] *= v[j];
+        }
     }
     if (p.epilogue == EPI_SWIGLU) {   // rows f0..f0+7 are gates, f0+8..f0+15 their up rows; N is a multiple of 16
         float a[8];
@@ -873,7 +884,8 @@ XS_API int64_t xs_gemm_tc_scratch_bytes(int T, int N, int ksplit) {
     return tiles * ksplit * BM * bn * (int64_t)sizeof(float) + 65536;
 }
 
-// epilogue: 0 store (out_dtype), 1 residual (out is float32 [T, N], += result), 2 SwiGLU (out is [T, N / 2]).
+// epilogue: 0 store (out_dtype), 1 residual (out is float32 [T, N], += result), 2 SwiGLU (out is [T, N / 2]),
+// 3 store max(result, 0)^2.
 // ksplit > 1: scratch of xs_gemm_tc_scratch_bytes; its last 64 KiB are counters that are zero between calls.
 // status: one device int that the kernel sets non-zero if a wait inside it gave up (the result is then invalid).
 static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* out, int out_dtype, int epilogue, int T, int N,
@@ -883,7 +895,8 @@ static int gemm_tc_impl(const void* x, const void* w, const float* bias, void* o
     XS_REQUIRE(xs_gemm_tc_supports(T, N, K, ldx, ldw), "gemm (tcgen05): T %d, N %d, K %d, strides %lld, %lld not supported", T,
                N, K, (long long)ldx, (long long)ldw);
     XS_REQUIRE(((uintptr_t)x % 16 == 0) && ((uintptr_t)w % 16 == 0), "gemm (tcgen05): operands must be 16-byte aligned");
-    XS_REQUIRE(epilogue >= 0 && epilogue <= 2 && status != nullptr && out != nullptr, "gemm (tcgen05): bad arguments");
+    XS_REQUIRE(epilogue >= 0 && epilogue <= 3 && status != nullptr && out != nullptr, "gemm (tcgen05): bad arguments");
+    XS_REQUIRE(epilogue != EPI_RELU_SQ || ksplit == 1, "gemm (tcgen05): the squared ReLU is applied to whole sums (one K slice)");
     XS_REQUIRE(epilogue != EPI_SWIGLU || N % 16 == 0, "gemm (tcgen05): the fused activation needs N %% 16 == 0");
     XS_REQUIRE(epilogue != EPI_RESIDUAL || out_dtype == XS_F32, "gemm (tcgen05): the residual is float32");
     XS_REQUIRE(ksplit >= 1 && ksplit <= 64, "gemm (tcgen05): %d K slices", ksplit);

@@ -9,39 +9,48 @@
 //     o  = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6)
 // The gates, the maximum, the state and every sum are float32 whatever the element type of q, k and v.
 //
-// One CTA walks the tokens of one (sequence, head) in order. Thread j keeps column j of S in registers, the thread behind the
-// last column keeps n (the column that a value of 1 would make), so S'^T q and n' . q are the same loop. Heads of more than
-// 224 value columns are cut over several CTAs, each with its own copy of n and m (the state has room for the copies). Tokens are staged in shared
-// memory eight at a time; the first warp turns their pre-activations into (a, b, exp(-m')): the transcendental functions
-// lane by lane, the maximum's recurrence by shuffles in order. The state is read from the sequence's slot before the
-// first token and written back behind the last.
+// One CTA walks the tokens of one (sequence, head, block of up to 64 value columns) in order, eight tokens at a time through
+// two buffers in shared memory. Its first warp is the producer: it stages the next eight tokens' q and k, turns their gate
+// pre-activations into (a, b) (the transcendental functions lane by lane, the maximum's recurrence by shuffles in order),
+// carries n (spread over its lanes: lane l keeps n[l], n[l + 32], ...) and leaves each token's denominator
+// max(|n' . q|, exp(-m')) + 1e-6. The other warps are consumers. A tile of S (a quarter of its rows x 32 columns) belongs to
+// one consumer warp, lane j keeping its rows of one column in registers (a few registers a lane, and four times the warps of
+// a column a lane: the recurrence is a chain of dependent operations per state entry, so what fills the pipes is warps).
+// While the producer works on the next tokens, a consumer runs S' = a S + b k v on its tile and leaves its quarter of
+// S'^T q for each token in shared memory; the quarters are added, divided and stored one buffer later. Each CTA has its own
+// copy of n and m (the state has room for one copy per block of columns), so that no CTA waits for another. The state is read
+// from the sequence's slot before the first token and written back behind the last.
 #include "common.cuh"
 
 namespace {
 
-constexpr int CH = 8;
+constexpr int CH = 8;              // tokens a buffer
+constexpr int RG = 4;              // row groups: consumer warps that share a block of 32 columns
+constexpr int MAX_CW = 2;          // blocks of 32 value columns a CTA
+constexpr int COLS = 32 * MAX_CW;
 
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
 template <typename TX, int DP>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(32 * (MAX_CW * RG + 1))
 mlstm_scan_kernel(const TX* __restrict__ qkv, int64_t ld, int q_col, int k_col, int v_col, const float* __restrict__ gates,
                   int64_t ldg, const float* __restrict__ i_bias, const float* __restrict__ f_bias, float* __restrict__ s_state,
                   float* __restrict__ nm_state, const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ slots,
-                  float* __restrict__ y, int H, int D, int Dv, int cols, float cap, float q_scale) {
-    extern __shared__ float sm[];
-    float* q_s = sm;                     // [CH, D]
-    float* k_s = q_s + CH * D;           // [CH, D]
-    float* v_s = k_s + CH * D;           // [CH, cols]
-    float* a_s = v_s + CH * cols;          // [CH]
-    float* b_s = a_s + CH;
-    float* e_s = b_s + CH;               // exp(-m')
-    float* nq_s = e_s + CH;              // n' . q
-    __shared__ float m_last;
-    // this CTA's value columns: col0 .. col0 + nv - 1 (thread j < nv), and its own copy of n (thread nv)
-    const int seq = blockIdx.x, head = blockIdx.y, j = threadIdx.x;
-    const int col0 = blockIdx.z * cols, nv = min(cols, Dv - col0), Z = gridDim.z;
-    const int lane = threadIdx.x & 31;
+                  float* __restrict__ y, int H, int D, int Dv, float cap, float q_scale) {
+    constexpr int DR = DP / RG;                 // rows of S a consumer lane keeps
+    constexpr int NR = (DP + 31) / 32;          // entries of n a producer lane keeps
+    __shared__ __align__(16) float q_s[2][CH][DP];
+    __shared__ __align__(16) float k_s[2][CH][DP];
+    __shared__ float part_s[2][RG][CH][COLS];
+    __shared__ float a_s[2][CH], b_s[2][CH], den_s[3][CH];
+    const int seq = blockIdx.x, head = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const bool producer = warp == 0;
+    const int cw = (warp - 1) / RG, rg = (warp - 1) % RG;          // consumers: block of columns, row group
+    const int n_consumers = (int)blockDim.x - 32;                   // consumer threads
+    const int col0 = blockIdx.z * COLS, Z = gridDim.z;
+    const int col = col0 + cw * 32 + lane;
+    const bool has_col = !producer && col < Dv;
+    const int row0 = rg * DR;
     pdl_launch_dependents();
     const int t_begin = cu_seqlens[seq], t_end = cu_seqlens[seq + 1];
     const int64_t slot = slots[seq];
@@ -50,97 +59,161 @@ mlstm_scan_kernel(const TX* __restrict__ qkv, int64_t ld, int q_col, int k_col, 
     if (t_end <= t_begin) return;
     float* s_mine = s_state + ((slot * H + head) * D) * (int64_t)Dv;
     float* nm_mine = nm_state + ((slot * H + head) * Z + blockIdx.z) * (int64_t)(D + 1);
-    float S[DP];
-#pragma unroll
-    for (int d = 0; d < DP; ++d) S[d] = 0.0f;
-    if (j < nv) {
-#pragma unroll
-        for (int d = 0; d < DP; ++d)
-            if (d < D) S[d] = s_mine[(int64_t)d * Dv + col0 + j];
-    } else if (j == nv) {
-#pragma unroll
-        for (int d = 0; d < DP; ++d)
-            if (d < D) S[d] = nm_mine[d];
-    }
-    float m = nm_mine[D];            // (only the first warp follows it)
+    const TX* v_mine = qkv + v_col + head * Dv + (has_col ? col : 0);
     const int HV = H * Dv;
-    for (int c0 = t_begin; c0 < t_end; c0 += CH) {
-        const int nc = min(CH, t_end - c0);
-        for (int idx = threadIdx.x; idx < nc * D; idx += blockDim.x) {
-            const int c = idx / D, d = idx - c * D;
-            const TX* row = qkv + (int64_t)(c0 + c) * ld + head * D + d;
-            q_s[idx] = to_f32(row[q_col]) * q_scale;
-            k_s[idx] = to_f32(row[k_col]);
+    float S[DR], n[NR];
+    TX vn[CH];
+    float m = 0.0f;
+    if (producer) {
+#pragma unroll
+        for (int r = 0; r < NR; ++r) n[r] = lane + 32 * r < D ? nm_mine[lane + 32 * r] : 0.0f;
+        m = nm_mine[D];
+        for (int idx = lane; idx < 2 * CH * DP; idx += 32) {        // the rows' padding stays zero from here on
+            (&q_s[0][0][0])[idx] = 0.0f;
+            (&k_s[0][0][0])[idx] = 0.0f;
         }
-        for (int idx = threadIdx.x; idx < nc * nv; idx += blockDim.x) {
-            const int c = idx / nv, d = idx - c * nv;
-            v_s[c * cols + d] = to_f32(qkv[(int64_t)(c0 + c) * ld + v_col + head * Dv + col0 + d]);
+        __syncwarp();
+    } else {
+#pragma unroll
+        for (int d = 0; d < DR; ++d) S[d] = (has_col && row0 + d < D) ? s_mine[(int64_t)(row0 + d) * Dv + col] : 0.0f;
+    }
+
+    // the producer's work on the tokens [c0, c0 + nc) into buffer `buf` (denominators into `dbuf`)
+    auto stage = [&](int c0, int nc, int buf, int dbuf) {
+        // every load of the eight tokens is issued before the first is used: the producer waits for memory once a buffer
+        TX qr[CH][NR], kr[CH][NR];
+        float zi = 0.0f, zf = 0.0f;
+        if (lane < nc) {
+            const float* g = gates + (int64_t)(c0 + lane) * ldg;
+            zi = g[head];
+            zf = g[H + head];
         }
-        if (threadIdx.x < 32) {
-            float gi = 0.0f, gf = 0.0f;
-            if (lane < nc) {
-                const float* g = gates + (int64_t)(c0 + lane) * ldg;
-                gi = cap * tanhf((g[head] + bi) / cap);
-                gf = log_sigmoid_f(cap * tanhf((g[H + head] + bf) / cap));
-            }
-            float m_before = 0.0f, m_after = 0.0f;
-            for (int c = 0; c < nc; ++c) {
-                const float fc = __shfl_sync(0xffffffffu, gf, c), ic = __shfl_sync(0xffffffffu, gi, c);
-                const float mn = fmaxf(fc + m, ic);
-                if (lane == c) {
-                    m_before = m;
-                    m_after = mn;
-                }
-                m = mn;
-            }
-            if (lane < nc) {
-                a_s[lane] = expf(gf + m_before - m_after);
-                b_s[lane] = expf(gi - m_after);
-                e_s[lane] = expf(-m_after);
-            }
-            if (lane == 0) m_last = m;
-        }
-        __syncthreads();
-        float acc[CH];
-        const bool is_n = j == nv;
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
-            acc[c] = 0.0f;
-            if (c < nc) {
-                const float a = a_s[c];
-                const float bv = b_s[c] * (is_n ? 1.0f : (j < nv ? v_s[c * cols + j] : 0.0f));
-                const float* kc = k_s + c * D;
-                const float* qc = q_s + c * D;
-                float sum = 0.0f;
 #pragma unroll
-                for (int d = 0; d < DP; ++d) {
-                    if (d < D) {
-                        S[d] = fmaf(a, S[d], bv * kc[d]);
-                        sum = fmaf(S[d], qc[d], sum);
-                    }
+            for (int r = 0; r < NR; ++r) {
+                const int d = lane + 32 * r;
+                if (c < nc && d < D) {
+                    const TX* row = qkv + (int64_t)(c0 + c) * ld + head * D + d;
+                    qr[c][r] = row[q_col];
+                    kr[c][r] = row[k_col];
                 }
-                acc[c] = sum;
-                if (is_n) nq_s[c] = sum;
             }
         }
-        __syncthreads();
-        if (j < nv) {
-#pragma unroll
-            for (int c = 0; c < CH; ++c)
-                if (c < nc)
-                    y[(int64_t)(c0 + c) * HV + head * Dv + col0 + j] = acc[c] / (fmaxf(fabsf(nq_s[c]), e_s[c]) + 1e-6f);
+        const float gi = cap * tanhf((zi + bi) / cap);
+        const float gf = log_sigmoid_f(cap * tanhf((zf + bf) / cap));
+        float m_before = 0.0f, m_after = 0.0f;
+        for (int c = 0; c < nc; ++c) {
+            const float fc = __shfl_sync(0xffffffffu, gf, c), ic = __shfl_sync(0xffffffffu, gi, c);
+            const float mn = fmaxf(fc + m, ic);
+            if (lane == c) {
+                m_before = m;
+                m_after = mn;
+            }
+            m = mn;
         }
-        __syncthreads();      // the next tokens overwrite what was just read
+        const float a_mine = expf(gf + m_before - m_after), b_mine = expf(gi - m_after), e_mine = expf(-m_after);
+        if (lane < nc) {
+            a_s[buf][lane] = a_mine;
+            b_s[buf][lane] = b_mine;
+        }
+        // n' = a n + b k and this lane's part of n' . q, token by token on the lane's own entries; the sums over the lanes after
+        float part[CH];
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            part[c] = 0.0f;
+            if (c < nc) {
+                const float a = __shfl_sync(0xffffffffu, a_mine, c), b = __shfl_sync(0xffffffffu, b_mine, c);
+#pragma unroll
+                for (int r = 0; r < NR; ++r) {
+                    const int d = lane + 32 * r;
+                    if (d < D) {
+                        const float qd = to_f32(qr[c][r]) * q_scale, kd = to_f32(kr[c][r]);
+                        q_s[buf][c][d] = qd;
+                        k_s[buf][c][d] = kd;
+                        n[r] = fmaf(a, n[r], b * kd);
+                        part[c] = fmaf(n[r], qd, part[c]);
+                    }
+                }
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int c = 0; c < CH; ++c) part[c] += __shfl_xor_sync(0xffffffffu, part[c], o);
+        }
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+            const float e = __shfl_sync(0xffffffffu, e_mine, c);
+            if (lane == 0 && c < nc) den_s[dbuf][c] = fmaxf(fabsf(part[c]), e) + 1e-6f;
+        }
+    };
+    auto load_values = [&](int c0, int nc) {
+#pragma unroll
+        for (int c = 0; c < CH; ++c)
+            if (has_col && c < nc) vn[c] = v_mine[(int64_t)(c0 + c) * ld];
+    };
+    // the consumers' last step for the tokens [c0, c0 + nc): the row groups' quarters added, divided, stored
+    auto finish = [&](int c0, int nc, int buf, int dbuf) {
+        const int cols_here = min(COLS, Dv - col0);
+        for (int idx = (int)threadIdx.x - 32; idx < nc * cols_here; idx += n_consumers) {
+            const int c = idx / cols_here, j = idx - c * cols_here;
+            const float sum = (part_s[buf][0][c][j] + part_s[buf][1][c][j]) + (part_s[buf][2][c][j] + part_s[buf][3][c][j]);
+            y[(int64_t)(c0 + c) * HV + head * Dv + col0 + j] = sum / den_s[dbuf][c];
+        }
+    };
+
+    if (producer) stage(t_begin, min(CH, t_end - t_begin), 0, 0);
+    else load_values(t_begin, min(CH, t_end - t_begin));
+    __syncthreads();
+    int buf = 0, chunk = 0;
+    for (int c0 = t_begin; c0 < t_end; c0 += CH, buf ^= 1, ++chunk) {
+        const int nc = min(CH, t_end - c0), next = c0 + CH;
+        if (producer) {
+            if (next < t_end) stage(next, min(CH, t_end - next), buf ^ 1, (chunk + 1) % 3);
+        } else {
+            TX v[CH];
+#pragma unroll
+            for (int c = 0; c < CH; ++c) v[c] = vn[c];
+            if (next < t_end) load_values(next, min(CH, t_end - next));
+            if (chunk > 0) finish(c0 - CH, CH, buf ^ 1, (chunk + 2) % 3);      // the tokens before these (their denominators: chunk - 1)
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+                if (c < nc) {
+                    const float a = a_s[buf][c], bv = has_col ? b_s[buf][c] * to_f32(v[c]) : 0.0f;
+                    float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                    for (int d = 0; d < DR; d += 4) {
+                        const float4 k4 = *reinterpret_cast<const float4*>(&k_s[buf][c][row0 + d]);
+                        const float4 q4 = *reinterpret_cast<const float4*>(&q_s[buf][c][row0 + d]);
+                        S[d] = fmaf(a, S[d], bv * k4.x);
+                        S[d + 1] = fmaf(a, S[d + 1], bv * k4.y);
+                        S[d + 2] = fmaf(a, S[d + 2], bv * k4.z);
+                        S[d + 3] = fmaf(a, S[d + 3], bv * k4.w);
+                        sum[0] = fmaf(S[d], q4.x, sum[0]);
+                        sum[1] = fmaf(S[d + 1], q4.y, sum[1]);
+                        sum[2] = fmaf(S[d + 2], q4.z, sum[2]);
+                        sum[3] = fmaf(S[d + 3], q4.w, sum[3]);
+                    }
+                    part_s[buf][rg][c][cw * 32 + lane] = (sum[0] + sum[1]) + (sum[2] + sum[3]);
+                }
+            }
+        }
+        __syncthreads();      // the next tokens are staged, and these are done with
     }
-    if (j < nv) {
+    if (!producer) {
+        const int last = t_begin + (chunk - 1) * CH;
+        finish(last, t_end - last, buf ^ 1, (chunk + 2) % 3);
+    }
+    if (producer) {
 #pragma unroll
-        for (int d = 0; d < DP; ++d)
-            if (d < D) s_mine[(int64_t)d * Dv + col0 + j] = S[d];
-    } else if (j == nv) {
+        for (int r = 0; r < NR; ++r)
+            if (lane + 32 * r < D) nm_mine[lane + 32 * r] = n[r];
+        if (lane == 0) nm_mine[D] = m;
+    } else if (has_col) {
 #pragma unroll
-        for (int d = 0; d < DP; ++d)
-            if (d < D) nm_mine[d] = S[d];
-        nm_mine[D] = m_last;
+        for (int d = 0; d < DR; ++d)
+            if (row0 + d < D) s_mine[(int64_t)(row0 + d) * Dv + col] = S[d];
     }
 }
 
@@ -150,7 +223,7 @@ mlstm_scan_kernel(const TX* __restrict__ qkv, int64_t ld, int q_col, int k_col, 
 // gates: [T, ldg] float32, the input gates' pre-activations in columns 0 .. H - 1 and the forget gates' in H .. 2 H - 1
 // (without their biases). s_state: [slots, H, D, Dv] and nm_state: [slots, H, Z, D + 1] (n, then m; Z = xs_mlstm_copies(Dv))
 // float32. y: [T, H * Dv] float32.
-XS_API int xs_mlstm_copies(int Dv) { return (Dv + 223) / 224; }
+XS_API int xs_mlstm_copies(int Dv) { return (Dv + COLS - 1) / COLS; }
 
 XS_API int xs_mlstm_scan(const void* qkv, int64_t ld, int q_col, int k_col, int v_col, const float* gates, int64_t ldg,
                          const float* i_bias, const float* f_bias, float* s_state, float* nm_state, const int32_t* cu_seqlens,
@@ -161,18 +234,13 @@ XS_API int xs_mlstm_scan(const void* qkv, int64_t ld, int q_col, int k_col, int 
                D, Dv, (double)cap);
     XS_REQUIRE(D <= 128, "mlstm: key size %d (at most 128)", D);
     const int Z = xs_mlstm_copies(Dv);
-    const int cols = (Dv + Z - 1) / Z;
     XS_REQUIRE(H <= 65535 && Z <= 65535, "mlstm: %d heads, %d column blocks exceed the grid limit", H, Z);
-    const int threads = ((cols + 1 + 31) / 32) * 32;
-    const size_t smem = (size_t)(CH * (2 * D + cols) + 4 * CH) * sizeof(float);
     const dim3 grid(n_seqs, H, Z);
-#define XS_GO(TT, DP)                                                                                                      \
-    do {                                                                                                                   \
-        if (smem > 48 * 1024)                                                                                              \
-            cudaFuncSetAttribute(mlstm_scan_kernel<TT, DP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
-        xs_launch(mlstm_scan_kernel<TT, DP>, grid, dim3(threads), smem, stream, (const TT*)qkv, ld, q_col, k_col, v_col,  \
-                  gates, ldg, i_bias, f_bias, s_state, nm_state, cu_seqlens, slots, y, H, D, Dv, cols, cap, q_scale);      \
-    } while (0)
+    const int blocks = Dv >= COLS ? MAX_CW : (Dv + 31) / 32;      // blocks of 32 columns in a CTA (all CTAs alike)
+    const int threads = 32 * (1 + blocks * RG);
+#define XS_GO(TT, DP)                                                                                                  \
+    xs_launch(mlstm_scan_kernel<TT, DP>, grid, dim3(threads), 0, stream, (const TT*)qkv, ld, q_col, k_col, v_col, gates,  \
+              ldg, i_bias, f_bias, s_state, nm_state, cu_seqlens, slots, y, H, D, Dv, cap, q_scale)
 #define XS_BY_D(TT)                      \
     do {                                 \
         if (D <= 16) XS_GO(TT, 16);      \

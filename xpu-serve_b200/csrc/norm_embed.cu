@@ -82,18 +82,26 @@ __global__ void embed_pair_kernel(const TW* __restrict__ table, const TW* __rest
     const TW* er = table + (int64_t)tok * H;
     const TW* pr = pair + bucket * H;
     float ss = 0.0f;
-    for (int c = threadIdx.x; c < H; c += blockDim.x) {
-        const float angle = (float)pos * inv_freq[c >> 1];
-        const float v = to_f32(er[c]) * scale + to_f32(pr[c]) + ((c & 1) ? cosf(angle) : sinf(angle));
-        row[c] = v;
-        ss += v * v;
+    for (int i = threadIdx.x; 2 * i < H; i += blockDim.x) {          // a thread takes the sine and the cosine of one angle
+        float sn, cs;
+        sincosf((float)pos * inv_freq[i], &sn, &cs);
+        const int c = 2 * i;
+        const float v0 = to_f32(er[c]) * scale + to_f32(pr[c]) + sn;
+        row[c] = v0;
+        ss += v0 * v0;
+        if (c + 1 < H) {
+            const float v1 = to_f32(er[c + 1]) * scale + to_f32(pr[c + 1]) + cs;
+            row[c + 1] = v1;
+            ss += v1 * v1;
+        }
     }
     float* out = h + (int64_t)t * H;
     if (w == nullptr) {
+        __syncthreads();
         for (int c = threadIdx.x; c < H; c += blockDim.x) out[c] = row[c];
         return;
     }
-    ss = block_sum(ss, scratch);
+    ss = block_sum(ss, scratch);          // (its barriers also order the row's writes before the reads below)
     const float inv = 1.0f / sqrtf(ss / (float)H + eps);
     for (int c = threadIdx.x; c < H; c += blockDim.x) out[c] = row[c] * inv * w[c];
 }

@@ -620,7 +620,7 @@ def gemm_small_m_rope(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias:
         page_size, float(eps), _stream()))
 
 
-EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+EPI_STORE, EPI_RESIDUAL, EPI_SWIGLU, EPI_RELU_SQ = 0, 1, 2, 3
 _tc_status = {}
 
 
@@ -678,7 +678,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: Optional[
             epilogue: int = EPI_STORE, ksplit: int = 1, scratch: Optional[torch.Tensor] = None) -> None:
     """x[T, K] . w[N, K]^T on tcgen05 tensor cores (bfloat16 operands). epilogue EPI_STORE: out[T, N] bfloat16 or
     float32; EPI_RESIDUAL: out float32 += product; EPI_SWIGLU: out[T, N / 2] = silu(gate) * up for a weight stacked
-    in blocks of 8 gate and 8 up rows."""
+    in blocks of 8 gate and 8 up rows; EPI_RELU_SQ: out = max(product, 0)^2."""
     for t, name in ((x, "x"), (w, "w")):
         if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or t.dtype != torch.bfloat16:
             raise KernelError(f"gemm (tcgen05): {name} must be a bfloat16 CUDA matrix with contiguous rows")

@@ -76,9 +76,13 @@ class SquaredRelu(FeedForward):
 
     def forward(self, y, step) -> torch.Tensor:
         rt = self.rt
-        up = rt.linear(y, self.w_up, "ffn_up")
         act = rt.ws.get("ffn_act", (y.shape[0], self.spec.intermediate), rt.act_dtype)
-        ops.relu_squared(up, act)
+        if rt.tensor_core_product(y, self.w_up, fused=True):
+            # long prompts: the activation in the tcgen05 product's epilogue (no pass of its own over the wide rows)
+            ops.gemm_tc(y, self.w_up, act, epilogue=ops.EPI_RELU_SQ)
+        else:
+            up = rt.linear(y, self.w_up, "ffn_up")
+            ops.relu_squared(up, act)
         return rt.linear(act, self.w_down, "ffn_out")
 
 

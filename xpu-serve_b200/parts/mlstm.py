@@ -24,8 +24,8 @@ from .base import Mixer, StateNeed, TensorSpec
 
 
 def _copies(vdim: int) -> int:
-    """Copies of n and m the kernel keeps per head: one per block of at most 224 value columns (csrc/mlstm.cu)."""
-    return (vdim + 223) // 224
+    """Copies of n and m the kernel keeps per head: one per block of 64 value columns (csrc/mlstm.cu)."""
+    return (vdim + 63) // 64
 
 
 class MLstmMixer(Mixer):
