@@ -175,9 +175,19 @@ def test_long_decoding(name, dtype, replayers, folders):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_prompts(dtype, replayers, folders):
-    """Prompts of 300 and 520 tokens beside one of 46 in one step, then single tokens."""
+    """Prompts of 300 and 520 tokens beside one of 46 in one step, then single tokens: the recurrent layers cut the long
+    ones into chunks of 128 that run side by side (three and five, the last ones partly filled), each sequence's state
+    carried from chunk to chunk and on into the single tokens that follow."""
+    from xpu_serve_b200.ops import lib as ops
     reqs = {"a": tiny.prompt("C", 306, salt=5), "b": tiny.prompt("C", 526, salt=6), "c": tiny.prompt("C", 46, salt=7)}
-    check("C", dtype, tu.batch_trace(reqs, 3, prompt_frac=0.985), reqs, replayers, folders, max_tokens=1280)
+    seen = []
+    real = ops.mlstm_scan
+    ops.mlstm_scan = lambda *a, **k: (seen.append(a[-1] if len(a) == 18 else k.get("chunks")), real(*a, **k))[1]
+    try:
+        check("C", dtype, tu.batch_trace(reqs, 3, prompt_frac=0.985), reqs, replayers, folders, max_tokens=1280)
+    finally:
+        ops.mlstm_scan = real
+    assert any(c is not None and c[0].shape[0] == 3 + 5 + 1 for c in seen), "the long prompts did not take the chunked scan"
 
 
 def test_every_product_on_the_tcgen05_kernel(folders, monkeypatch):
@@ -420,6 +430,53 @@ def test_mlstm_kernel_alone(H, D, Dv, dtype):
     # slots that no sequence of the launch used are untouched
     for free in (2, 5):
         assert torch.equal(S[free].cpu(), S0[free]) and torch.equal(nm[free].cpu(), nm0[free])
+
+
+@pytest.mark.parametrize("H,D,Dv,chunk", [(3, 10, 14, 7), (2, 64, 70, 128), (1, 128, 32, 50)])
+def test_mlstm_kernel_in_chunks(H, D, Dv, chunk):
+    """Sequences of 300, 46 and 520 tokens cut into chunks that run side by side (a pass from the empty state, the carry,
+    a pass from each chunk's true state), from states that are not zero: outputs and end states against the plain
+    recurrence run token by token. Forget gates near 0 and near 1 and input gates of both signs, so that the maximum is
+    now carried from before the chunk, now set inside it."""
+    from xpu_serve_b200.ops import lib as ops
+    rng = np.random.default_rng(H + D + chunk)
+    q_lens, slots = [300, 46, 520], [2, 0, 3]
+    T, Z, cap, scale = sum(q_lens), ops.mlstm_copies(Dv), 6.0, 0.4
+    ld = 2 * H * D + H * Dv
+    proj = torch.from_numpy(rng.standard_normal((T, ld)) * 0.7).float()
+    gates = torch.from_numpy(rng.standard_normal((T, 2 * H)) * 4.0).float()
+    bi, bf = torch.from_numpy(rng.uniform(-1, 1, H)).float(), torch.from_numpy(rng.uniform(0, 3, H)).float()
+    S0 = torch.from_numpy(rng.standard_normal((4, H, D, Dv)) * 0.5).float()
+    n0 = torch.from_numpy(rng.standard_normal((4, H, D)) * 0.5).float()
+    m0 = torch.from_numpy(rng.uniform(-2, 4, (4, H))).float()
+    nm0 = torch.cat([n0, m0[..., None]], -1)[:, :, None, :].repeat(1, 1, Z, 1).contiguous()
+    cu = [0] + list(np.cumsum(q_lens))
+    rows, first = [], [0]
+    for i, (b, e) in enumerate(zip(cu[:-1], cu[1:])):
+        rows += [(i, t, min(chunk, e - t)) for t in range(b, e, chunk)]
+        first.append(len(rows))
+    dev = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    S, nm = S0.clone().cuda(), nm0.clone().cuda()
+    y = torch.zeros(T, H * Dv, device="cuda")
+    scratch = (dev(rows), dev(first), torch.empty(len(rows), H, D, Dv, device="cuda"), torch.empty(len(rows), H, Z, D + 2, device="cuda"))
+    ops.mlstm_scan(proj.cuda(), 0, H * D, 2 * H * D, gates.cuda(), bi.cuda(), bf.cuda(), S, nm, dev(cu), dev(slots), y, H, D, Dv,
+                   cap, scale, scratch)
+    torch.cuda.synchronize()
+    P = proj.double().numpy()
+    tol = 1e-4
+    for s, (b, e) in enumerate(zip(cu[:-1], cu[1:])):
+        for h in range(H):
+            ref, Sr, nr, mr = plain_mlstm(P[b:e, h * D:(h + 1) * D] * scale, P[b:e, H * D + h * D:H * D + (h + 1) * D],
+                                          P[b:e, 2 * H * D + h * Dv:2 * H * D + (h + 1) * Dv], gates[b:e, h].double().numpy(),
+                                          gates[b:e, H + h].double().numpy(), float(bi[h]), float(bf[h]), cap,
+                                          S0[slots[s], h].double().numpy(), n0[slots[s], h].double().numpy(), float(m0[slots[s], h]))
+            g = y[b:e, h * Dv:(h + 1) * Dv].double().cpu().numpy()
+            assert np.abs(g - ref).max() <= tol * max(np.abs(ref).max(), 1.0), (s, h, np.abs(g - ref).max())
+            assert np.abs(S[slots[s], h].double().cpu().numpy() - Sr).max() <= tol * max(np.abs(Sr).max(), 1.0)
+            for z in range(Z):
+                assert np.abs(nm[slots[s], h, z, :D].double().cpu().numpy() - nr).max() <= tol * max(np.abs(nr).max(), 1.0)
+                assert abs(float(nm[slots[s], h, z, D]) - mr) <= 1e-4 * max(abs(mr), 1.0)
+    assert torch.equal(S[1].cpu(), S0[1]) and torch.equal(nm[1].cpu(), nm0[1])       # a slot that no sequence used
 
 
 def test_embedding_alone():

@@ -32,18 +32,26 @@ constexpr int COLS = 32 * MAX_CW;
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
 template <typename TX, int DP>
-__global__ void __launch_bounds__(32 * (MAX_CW * RG + 1))
+__global__ void __launch_bounds__(32 * (MAX_CW * RG + 1), DP <= 64 ? 2 : 1)
 mlstm_scan_kernel(const TX* __restrict__ qkv, int64_t ld, int q_col, int k_col, int v_col, const float* __restrict__ gates,
                   int64_t ldg, const float* __restrict__ i_bias, const float* __restrict__ f_bias, float* __restrict__ s_state,
                   float* __restrict__ nm_state, const int32_t* __restrict__ cu_seqlens, const int32_t* __restrict__ slots,
-                  float* __restrict__ y, int H, int D, int Dv, float cap, float q_scale) {
+                  float* __restrict__ y, int H, int D, int Dv, float cap, float q_scale, const int32_t* __restrict__ chunks,
+                  int mode, float* __restrict__ s_chunk, float* __restrict__ nm_chunk) {
     constexpr int DR = DP / RG;                 // rows of S a consumer lane keeps
     constexpr int NR = (DP + 31) / 32;          // entries of n a producer lane keeps
     __shared__ __align__(16) float q_s[2][CH][DP];
     __shared__ __align__(16) float k_s[2][CH][DP];
     __shared__ float part_s[2][RG][CH][COLS];
     __shared__ float a_s[2][CH], b_s[2][CH], den_s[3][CH];
-    const int seq = blockIdx.x, head = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // mode 0: blockIdx.x is a sequence, walked whole from its slot's state, which takes the end state.
+    // mode 1: blockIdx.x is a chunk (sequence, first token, tokens), walked from the empty state (S = 0, n = 0, m = -inf,
+    //         so that its first token's m is its own input gate); its end state and the sum of its log forget gates go
+    //         to s_chunk / nm_chunk [chunk] (nm rows of D + 2: n, m, sum), nothing else is written.
+    // mode 2: blockIdx.x is a chunk, walked from the state that s_chunk / nm_chunk [chunk] hold (what xs_mlstm_carry
+    //         left there: the sequence's state before the chunk); only y is written.
+    const int head = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int seq = mode == 0 ? (int)blockIdx.x : chunks[3 * blockIdx.x];
     const bool producer = warp == 0;
     const int cw = (warp - 1) / RG, rg = (warp - 1) % RG;          // consumers: block of columns, row group
     const int n_consumers = (int)blockDim.x - 32;                   // consumer threads
@@ -52,22 +60,26 @@ mlstm_scan_kernel(const TX* __restrict__ qkv, int64_t ld, int q_col, int k_col, 
     const bool has_col = !producer && col < Dv;
     const int row0 = rg * DR;
     pdl_launch_dependents();
-    const int t_begin = cu_seqlens[seq], t_end = cu_seqlens[seq + 1];
+    const int t_begin = mode == 0 ? cu_seqlens[seq] : chunks[3 * blockIdx.x + 1];
+    const int t_end = mode == 0 ? cu_seqlens[seq + 1] : t_begin + chunks[3 * blockIdx.x + 2];
     const int64_t slot = slots[seq];
     const float bi = i_bias[head], bf = f_bias[head];
     pdl_wait();
     if (t_end <= t_begin) return;
-    float* s_mine = s_state + ((slot * H + head) * D) * (int64_t)Dv;
-    float* nm_mine = nm_state + ((slot * H + head) * Z + blockIdx.z) * (int64_t)(D + 1);
+    float* s_mine = mode == 0 ? s_state + ((slot * H + head) * D) * (int64_t)Dv
+                              : s_chunk + (((int64_t)blockIdx.x * H + head) * D) * (int64_t)Dv;
+    float* nm_mine = mode == 0 ? nm_state + ((slot * H + head) * Z + blockIdx.z) * (int64_t)(D + 1)
+                               : nm_chunk + (((int64_t)blockIdx.x * H + head) * Z + blockIdx.z) * (int64_t)(D + 2);
+    const bool from_empty = mode == 1, keep_state = mode != 2, write_y = mode != 1;
     const TX* v_mine = qkv + v_col + head * Dv + (has_col ? col : 0);
     const int HV = H * Dv;
     float S[DR], n[NR];
     TX vn[CH];
-    float m = 0.0f;
+    float m = 0.0f, f_sum = 0.0f;
     if (producer) {
 #pragma unroll
-        for (int r = 0; r < NR; ++r) n[r] = lane + 32 * r < D ? nm_mine[lane + 32 * r] : 0.0f;
-        m = nm_mine[D];
+        for (int r = 0; r < NR; ++r) n[r] = (!from_empty && lane + 32 * r < D) ? nm_mine[lane + 32 * r] : 0.0f;
+        m = from_empty ? -INFINITY : nm_mine[D];
         for (int idx = lane; idx < 2 * CH * DP; idx += 32) {        // the rows' padding stays zero from here on
             (&q_s[0][0][0])[idx] = 0.0f;
             (&k_s[0][0][0])[idx] = 0.0f;
@@ -75,14 +87,17 @@ mlstm_scan_kernel(const TX* __restrict__ qkv, int64_t ld, int q_col, int k_col, 
         __syncwarp();
     } else {
 #pragma unroll
-        for (int d = 0; d < DR; ++d) S[d] = (has_col && row0 + d < D) ? s_mine[(int64_t)(row0 + d) * Dv + col] : 0.0f;
+        for (int d = 0; d < DR; ++d)
+            S[d] = (!from_empty && has_col && row0 + d < D) ? s_mine[(int64_t)(row0 + d) * Dv + col] : 0.0f;
     }
 
     // the producer's work on the tokens [c0, c0 + nc) into buffer `buf` (denominators into `dbuf`)
-    auto stage = [&](int c0, int nc, int buf, int dbuf) {
-        // every load of the eight tokens is issued before the first is used: the producer waits for memory once a buffer
-        TX qr[CH][NR], kr[CH][NR];
-        float zi = 0.0f, zf = 0.0f;
+    // The producer's loads run one buffer ahead of its arithmetic: `fetch` asks for eight tokens' q, k and gate
+    // pre-activations (every load issued before any is used), `stage` works on what the last fetch brought and then fetches
+    // the tokens after, so that memory is waited for under the consumers' work and not in the producer's own chain.
+    TX qr[CH][NR], kr[CH][NR];
+    float zi = 0.0f, zf = 0.0f;
+    auto fetch = [&](int c0, int nc) {
         if (lane < nc) {
             const float* g = gates + (int64_t)(c0 + lane) * ldg;
             zi = g[head];
@@ -100,17 +115,23 @@ mlstm_scan_kernel(const TX* __restrict__ qkv, int64_t ld, int q_col, int k_col, 
                 }
             }
         }
+    };
+    auto stage = [&](int c0, int nc, int buf, int dbuf) {
         const float gi = cap * tanhf((zi + bi) / cap);
         const float gf = log_sigmoid_f(cap * tanhf((zf + bf) / cap));
         float m_before = 0.0f, m_after = 0.0f;
-        for (int c = 0; c < nc; ++c) {
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
             const float fc = __shfl_sync(0xffffffffu, gf, c), ic = __shfl_sync(0xffffffffu, gi, c);
-            const float mn = fmaxf(fc + m, ic);
-            if (lane == c) {
-                m_before = m;
-                m_after = mn;
+            if (c < nc) {
+                const float mn = fmaxf(fc + m, ic);
+                if (lane == c) {
+                    m_before = m;
+                    m_after = mn;
+                }
+                m = mn;
+                f_sum += fc;
             }
-            m = mn;
         }
         const float a_mine = expf(gf + m_before - m_after), b_mine = expf(gi - m_after), e_mine = expf(-m_after);
         if (lane < nc) {
@@ -137,6 +158,7 @@ mlstm_scan_kernel(const TX* __restrict__ qkv, int64_t ld, int q_col, int k_col, 
                 }
             }
         }
+        if (c0 + nc < t_end) fetch(c0 + nc, min(CH, t_end - c0 - nc));      // (nc is CH here: only a sequence's last tokens are fewer)
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
 #pragma unroll
@@ -159,12 +181,14 @@ mlstm_scan_kernel(const TX* __restrict__ qkv, int64_t ld, int q_col, int k_col, 
         for (int idx = (int)threadIdx.x - 32; idx < nc * cols_here; idx += n_consumers) {
             const int c = idx / cols_here, j = idx - c * cols_here;
             const float sum = (part_s[buf][0][c][j] + part_s[buf][1][c][j]) + (part_s[buf][2][c][j] + part_s[buf][3][c][j]);
-            y[(int64_t)(c0 + c) * HV + head * Dv + col0 + j] = sum / den_s[dbuf][c];
+            if (write_y) y[(int64_t)(c0 + c) * HV + head * Dv + col0 + j] = sum / den_s[dbuf][c];
         }
     };
 
-    if (producer) stage(t_begin, min(CH, t_end - t_begin), 0, 0);
-    else load_values(t_begin, min(CH, t_end - t_begin));
+    if (producer) {
+        fetch(t_begin, min(CH, t_end - t_begin));
+        stage(t_begin, min(CH, t_end - t_begin), 0, 0);
+    } else load_values(t_begin, min(CH, t_end - t_begin));
     __syncthreads();
     int buf = 0, chunk = 0;
     for (int c0 = t_begin; c0 < t_end; c0 += CH, buf ^= 1, ++chunk) {
@@ -205,16 +229,63 @@ mlstm_scan_kernel(const TX* __restrict__ qkv, int64_t ld, int q_col, int k_col, 
         const int last = t_begin + (chunk - 1) * CH;
         finish(last, t_end - last, buf ^ 1, (chunk + 2) % 3);
     }
+    if (!keep_state) return;
     if (producer) {
 #pragma unroll
         for (int r = 0; r < NR; ++r)
             if (lane + 32 * r < D) nm_mine[lane + 32 * r] = n[r];
-        if (lane == 0) nm_mine[D] = m;
+        if (lane == 0) {
+            nm_mine[D] = m;
+            if (mode == 1) nm_mine[D + 1] = f_sum;
+        }
     } else if (has_col) {
 #pragma unroll
         for (int d = 0; d < DR; ++d)
             if (row0 + d < D) s_mine[(int64_t)(row0 + d) * Dv + col] = S[d];
     }
+}
+
+// Between the two passes over chunks: for every (sequence, head), chunk by chunk in order, the chunk's entry of s_chunk /
+// nm_chunk (its end state from the empty state: S_loc, n_loc, m_loc, and F, the sum of its log forget gates) is replaced by
+// the sequence's state before the chunk, and the slot's state moves on over the chunk:
+//     m' = max(m + F, m_loc);   S' = exp(m + F - m') S + exp(m_loc - m') S_loc;   n' likewise
+// which is what the token-by-token recurrence gives (its maximum unrolls to exactly this). Afterwards the slot holds the
+// state behind the step's last token.
+__global__ void mlstm_carry_kernel(float* __restrict__ s_state, float* __restrict__ nm_state, float* __restrict__ s_chunk,
+                                   float* __restrict__ nm_chunk, const int32_t* __restrict__ first_chunk,
+                                   const int32_t* __restrict__ slots, int H, int D, int Dv, int Z) {
+    pdl_launch_dependents();
+    const int seq = blockIdx.x, head = blockIdx.y;
+    const int64_t slot = slots[seq];
+    const int j0 = first_chunk[seq], j1 = first_chunk[seq + 1];
+    pdl_wait();
+    float* S = s_state + ((slot * H + head) * D) * (int64_t)Dv;
+    float* nm = nm_state + (slot * H + head) * (int64_t)Z * (D + 1);
+    const int n_s = D * Dv, n_n = Z * D;
+    float m = nm[D];                                      // (every copy holds the same m)
+    for (int j = j0; j < j1; ++j) {
+        float* Sl = s_chunk + (((int64_t)j * H + head) * D) * (int64_t)Dv;
+        float* nml = nm_chunk + ((int64_t)j * H + head) * (int64_t)Z * (D + 2);
+        const float m_loc = nml[D], F = nml[D + 1];
+        const float m_new = fmaxf(m + F, m_loc);
+        const float ca = expf(m + F - m_new), cb = expf(m_loc - m_new);
+        __syncthreads();                                  // every thread has read the chunk's m and F
+        for (int e = threadIdx.x; e < n_s; e += blockDim.x) {
+            const float loc = Sl[e], run = S[e];
+            Sl[e] = run;
+            S[e] = ca * run + cb * loc;
+        }
+        for (int e = threadIdx.x; e < n_n; e += blockDim.x) {
+            const int z = e / D, d = e - z * D;
+            const float loc = nml[z * (D + 2) + d], run = nm[z * (D + 1) + d];
+            nml[z * (D + 2) + d] = run;
+            nm[z * (D + 1) + d] = ca * run + cb * loc;
+        }
+        __syncthreads();
+        if ((int)threadIdx.x < Z) nml[threadIdx.x * (D + 2) + D] = m;       // the chunk starts from this m
+        m = m_new;
+    }
+    if ((int)threadIdx.x < Z) nm[threadIdx.x * (D + 1) + D] = m;
 }
 
 }  // namespace
@@ -225,9 +296,14 @@ mlstm_scan_kernel(const TX* __restrict__ qkv, int64_t ld, int q_col, int k_col, 
 // float32. y: [T, H * Dv] float32.
 XS_API int xs_mlstm_copies(int Dv) { return (Dv + COLS - 1) / COLS; }
 
+// With a chunk list (chunks [n_chunks, 3]: sequence, first token, tokens; first_chunk [n_seqs + 1]; s_chunk [n_chunks, H, D, Dv]
+// and nm_chunk [n_chunks, H, Z, D + 2] float32 scratch) the chunks run side by side: a pass from the empty state that leaves
+// each chunk's end state, a carry over each sequence's chunks in order, and a pass from each chunk's true state that writes y
+// (three launches, twice the recurrence's work, a sequence's tokens no longer one after another).
 XS_API int xs_mlstm_scan(const void* qkv, int64_t ld, int q_col, int k_col, int v_col, const float* gates, int64_t ldg,
                          const float* i_bias, const float* f_bias, float* s_state, float* nm_state, const int32_t* cu_seqlens,
                          const int32_t* slots, float* y, int n_seqs, int H, int D, int Dv, float cap, float q_scale, int dtype,
+                         const int32_t* chunks, const int32_t* first_chunk, int n_chunks, float* s_chunk, float* nm_chunk,
                          cudaStream_t stream) {
     if (n_seqs == 0) return 0;
     XS_REQUIRE(n_seqs > 0 && H > 0 && D > 0 && Dv > 0 && cap > 0.0f, "mlstm: %d sequences, %d heads of %d and %d, cap %g", n_seqs, H,
@@ -235,12 +311,16 @@ XS_API int xs_mlstm_scan(const void* qkv, int64_t ld, int q_col, int k_col, int 
     XS_REQUIRE(D <= 128, "mlstm: key size %d (at most 128)", D);
     const int Z = xs_mlstm_copies(Dv);
     XS_REQUIRE(H <= 65535 && Z <= 65535, "mlstm: %d heads, %d column blocks exceed the grid limit", H, Z);
-    const dim3 grid(n_seqs, H, Z);
+    const bool chunked = chunks != nullptr;
+    XS_REQUIRE(!chunked || (first_chunk != nullptr && n_chunks > 0 && s_chunk != nullptr && nm_chunk != nullptr),
+               "mlstm: a chunk list needs its index and its scratch");
+    dim3 grid(chunked ? n_chunks : n_seqs, H, Z);
+    int mode = chunked ? 1 : 0;
     const int blocks = Dv >= COLS ? MAX_CW : (Dv + 31) / 32;      // blocks of 32 columns in a CTA (all CTAs alike)
     const int threads = 32 * (1 + blocks * RG);
 #define XS_GO(TT, DP)                                                                                                  \
     xs_launch(mlstm_scan_kernel<TT, DP>, grid, dim3(threads), 0, stream, (const TT*)qkv, ld, q_col, k_col, v_col, gates,  \
-              ldg, i_bias, f_bias, s_state, nm_state, cu_seqlens, slots, y, H, D, Dv, cap, q_scale)
+              ldg, i_bias, f_bias, s_state, nm_state, cu_seqlens, slots, y, H, D, Dv, cap, q_scale, chunks, mode, s_chunk, nm_chunk)
 #define XS_BY_D(TT)                      \
     do {                                 \
         if (D <= 16) XS_GO(TT, 16);      \
@@ -249,8 +329,16 @@ XS_API int xs_mlstm_scan(const void* qkv, int64_t ld, int q_col, int k_col, int 
         else XS_GO(TT, 128);             \
     } while (0)
     XS_DISPATCH_DTYPE(dtype, TT, XS_BY_D(TT));
+    XS_LAUNCH_CHECK("mlstm_scan");
+    if (chunked) {
+        xs_launch(mlstm_carry_kernel, dim3(n_seqs, H), dim3(256), 0, stream, s_state, nm_state, s_chunk, nm_chunk, first_chunk,
+                  slots, H, D, Dv, Z);
+        XS_LAUNCH_CHECK("mlstm_carry");
+        mode = 2;
+        XS_DISPATCH_DTYPE(dtype, TT, XS_BY_D(TT));
+        XS_LAUNCH_CHECK("mlstm_scan (second pass)");
+    }
 #undef XS_BY_D
 #undef XS_GO
-    XS_LAUNCH_CHECK("mlstm_scan");
     return 0;
 }

@@ -66,7 +66,7 @@ def _signatures(lib) -> None:
         "xs_moe_combine": [P, P, P, P, I, I, I, P, P, I, I, P],
         "xs_relu_squared": [P, P, I, L, P],
         "xs_embed_pair": [P, P, I, P, P, P, P, P, P, P, P, P, I, I, F, I, ctypes.c_longlong, ctypes.c_longlong, F, P],
-        "xs_mlstm_scan": [P, L, I, I, I, P, L, P, P, P, P, P, P, P, I, I, I, I, F, F, I, P],
+        "xs_mlstm_scan": [P, L, I, I, I, P, L, P, P, P, P, P, P, P, I, I, I, I, F, F, I, P, P, I, P, P, P],
         "xs_latent_prepare": [P, L, P, L, P, P, P, P, P, I, P, P, I, I, I, I, I, I, I, F, I, I, P],
         "xs_latent_attention_generic": [P, L, L, P, P, P, I, P, P, P, L, P, P, L, L, I, I, I, I, I, F, I, I, P],
         "xs_gemm_batched": [P, L, L, P, L, L, P, L, L, I, I, I, I, I, P],
@@ -988,11 +988,14 @@ def mlstm_copies(vdim: int) -> int:
 
 def mlstm_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, gates: torch.Tensor, i_bias: torch.Tensor,
                f_bias: torch.Tensor, s_state: torch.Tensor, nm_state: torch.Tensor, cu_seqlens: torch.Tensor,
-               slots: torch.Tensor, y: torch.Tensor, heads: int, dim: int, vdim: int, cap: float, q_scale: float) -> None:
+               slots: torch.Tensor, y: torch.Tensor, heads: int, dim: int, vdim: int, cap: float, q_scale: float,
+               chunks=None) -> None:
     """The mLSTM recurrence over a step's tokens, sequence by sequence from each slot's state (csrc/mlstm.cu). qkv: rows
     with q [heads * dim] at column q_col, k at k_col, v [heads * vdim] at v_col; gates: float32 rows [input gates' |
     forget gates'] pre-activations without biases; s_state [slots, heads, dim, vdim], nm_state [slots, heads,
-    mlstm_copies(vdim), dim + 1] float32; y [T, heads * vdim] float32."""
+    mlstm_copies(vdim), dim + 1] float32; y [T, heads * vdim] float32. `chunks` (chunk list [n, 3] int32: sequence, first
+    token, tokens; first chunk of each sequence [sequences + 1] int32; scratch [n, heads, dim, vdim] and [n, heads,
+    mlstm_copies(vdim), dim + 2] float32): the chunks run side by side in two passes with a carry between them."""
     _need(gates, "gates", torch.float32); _need(y, "y", torch.float32); _need(s_state, "state", torch.float32)
     _need(nm_state, "normaliser state", torch.float32); _need(i_bias, "input gate bias", torch.float32)
     _need(f_bias, "forget gate bias", torch.float32)
@@ -1006,10 +1009,21 @@ def mlstm_scan(qkv: torch.Tensor, q_col: int, k_col: int, v_col: int, gates: tor
         raise KernelError(f"mlstm: state {tuple(s_state.shape)} / {tuple(nm_state.shape)} for {heads} heads of {dim} / {vdim}")
     if i_bias.numel() != heads or f_bias.numel() != heads:
         raise KernelError(f"mlstm: gate biases of {i_bias.numel()} / {f_bias.numel()} for {heads} heads")
+    chunk_args = (None, None, 0, None, None)
+    if chunks is not None:
+        chunk_seq, first_chunk, s_chunk, nm_chunk = chunks
+        n = chunk_seq.shape[0]
+        _need(chunk_seq, "chunk list", torch.int32); _need(first_chunk, "first chunks", torch.int32)
+        _need(s_chunk, "chunk states", torch.float32); _need(nm_chunk, "chunk normalisers", torch.float32)
+        if (tuple(s_chunk.shape) != (n, heads, dim, vdim) or tuple(nm_chunk.shape) != (n, heads, mlstm_copies(vdim), dim + 2)
+                or first_chunk.numel() != cu_seqlens.numel()):
+            raise KernelError(f"mlstm: chunk scratch {tuple(s_chunk.shape)} / {tuple(nm_chunk.shape)} for {n} chunks")
+        chunk_args = (chunk_seq.data_ptr(), first_chunk.data_ptr(), n, s_chunk.data_ptr(), nm_chunk.data_ptr())
     _check(load().xs_mlstm_scan(qkv.data_ptr(), qkv.stride(0), int(q_col), int(k_col), int(v_col), gates.data_ptr(),
                                 gates.stride(0), i_bias.data_ptr(), f_bias.data_ptr(), s_state.data_ptr(), nm_state.data_ptr(),
                                 cu_seqlens.data_ptr(), slots.data_ptr(), y.data_ptr(), cu_seqlens.numel() - 1, heads, dim, vdim,
-                                float(cap), float(q_scale), _code(qkv), _stream()))
+                                float(cap), float(q_scale), _code(qkv), *chunk_args, _stream()),
+           kernels=3 if chunks is not None else 1)
 
 
 # ----------------------------------------------------------------------------- latent attention

@@ -20,6 +20,23 @@ from ..ops import lib as ops
 from .base import Mixer, StateNeed, TensorSpec
 
 
+def chunk_plan(step, chunk: int, device):
+    """The step's tokens cut into chunks of at most `chunk`, on the device: ([chunks, 3] (sequence, first token, tokens),
+    [sequences + 1] first chunk of each), made once a step and shared by the step's layers (recurrent mixers that run
+    long pieces chunk by chunk side by side)."""
+    plans = step.__dict__.setdefault("_chunk_plans", {})
+    if chunk not in plans:
+        rows, first, t0 = [], [0], 0
+        for i, n in enumerate(int(v) for v in step.q_lens_host):
+            for c0 in range(0, n, chunk):
+                rows.append((i, t0 + c0, min(chunk, n - c0)))
+            first.append(len(rows))
+            t0 += n
+        plans[chunk] = (torch.from_numpy(np.asarray(rows, dtype=np.int32)).to(device),
+                        torch.from_numpy(np.asarray(first, dtype=np.int32)).to(device))
+    return plans[chunk]
+
+
 class Mamba2Mixer(Mixer):
     kind = "mamba2"
     fixed_shape_ok = True      # a step captured for any lengths walks its tokens in order (no plan from the host)
@@ -60,20 +77,7 @@ class Mamba2Mixer(Mixer):
         self.chunk = int(os.environ.get("XS_MAMBA2_CHUNK", "128"))
 
     def _plan(self, step):
-        """The step's tokens cut into chunks, on the device: ([chunks, 3] (sequence, first token, tokens),
-        [sequences + 1] first chunk of each), made once a step and shared by the step's layers."""
-        plans = step.__dict__.setdefault("_mamba2_plans", {})
-        if self.chunk not in plans:
-            rows, first, t0 = [], [0], 0
-            for i, n in enumerate(int(v) for v in step.q_lens_host):
-                for c0 in range(0, n, self.chunk):
-                    rows.append((i, t0 + c0, min(self.chunk, n - c0)))
-                first.append(len(rows))
-                t0 += n
-            dev = self.rt.device
-            plans[self.chunk] = (torch.from_numpy(np.asarray(rows, dtype=np.int32)).to(dev),
-                                 torch.from_numpy(np.asarray(first, dtype=np.int32)).to(dev))
-        return plans[self.chunk]
+        return chunk_plan(step, self.chunk, self.rt.device)
 
     def forward(self, x, step, cache) -> torch.Tensor:
         s, rt = self.spec, self.rt

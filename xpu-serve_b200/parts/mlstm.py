@@ -10,10 +10,13 @@ maximum m, all float32 and zero at a sequence's start. For a token with input x:
 then every head's o divided by its root mean square, times a weight over all heads, times sigmoid(Wg x), and the output
 projection. One product gives q, k, v and the output gate's logits in the activation type; the two gates' pre-activations
 come from a second product whose output is float32, and everything behind them (soft cap, logsigmoid, the maximum, the
-exponentials, the state and its sums, the heads' norm) is float32 in both precision modes (csrc/mlstm.cu).
+exponentials, the state and its sums, the heads' norm) is float32 in both precision modes (csrc/mlstm.cu). Single tokens
+and short pieces walk in order; long pieces of a prompt run chunk by chunk side by side (a pass from the empty state, a
+carry between the chunks, a second pass from each chunk's true state).
 """
 from __future__ import annotations
 
+import os
 from typing import Dict
 
 import torch
@@ -21,6 +24,7 @@ import torch
 from .. import registry
 from ..ops import lib as ops
 from .base import Mixer, StateNeed, TensorSpec
+from .mamba2 import chunk_plan
 
 
 def _copies(vdim: int) -> int:
@@ -68,6 +72,8 @@ class MLstmMixer(Mixer):
         self.f_bias = rt.vector(weights[n["f_bias"]])
         self.w_norm = rt.vector(weights[n["norm"]])
         self.w_o = rt.matrix(weights[n["o"]])
+        # pieces of at least two chunks run chunk by chunk side by side (XS_MLSTM_CHUNK tokens each; 0: always in order)
+        self.chunk = int(os.environ.get("XS_MLSTM_CHUNK", "128"))
 
     def forward(self, x, step, cache) -> torch.Tensor:
         s, rt = self.spec, self.rt
@@ -77,8 +83,16 @@ class MLstmMixer(Mixer):
         proj = rt.linear(x, self.w_in, "mlstm_proj")
         gates = rt.linear(x, self.w_gates, "mlstm_gates", out_dtype=torch.float32)
         y = rt.ws.get("mlstm_y", (T, vd), torch.float32)
+        chunks = None
+        if self.chunk > 0 and not step.fixed_shape and not step.decode and step.max_q_len >= 2 * self.chunk:
+            # a long piece: its chunks from the empty state side by side, a carry over them in order, then the chunks again
+            # from their true states (csrc/mlstm.cu)
+            chunk_seq, first_chunk = chunk_plan(step, self.chunk, rt.device)
+            n = chunk_seq.shape[0]
+            chunks = (chunk_seq, first_chunk, rt.ws.get("mlstm_chunk_state", (n, s.heads, s.dim, s.vdim), torch.float32),
+                      rt.ws.get("mlstm_chunk_nm", (n, s.heads, _copies(s.vdim), s.dim + 2), torch.float32))
         ops.mlstm_scan(proj, 0, qd, 2 * qd, gates, self.i_bias, self.f_bias, cache[0].storage, cache[1].storage,
-                       step.cu_seqlens, step.slots, y, s.heads, s.dim, s.vdim, s.gate_cap, float(s.dim) ** -0.5)
+                       step.cu_seqlens, step.slots, y, s.heads, s.dim, s.vdim, s.gate_cap, float(s.dim) ** -0.5, chunks)
         yn = rt.ws.get("mlstm_normed", (T, vd), rt.act_dtype)
         ops.grouped_rmsnorm(y, self.w_norm, yn, s.heads, s.eps, gate=proj[:, 2 * qd + vd:])
         return rt.linear(yn, self.w_o, "mixer_out")
