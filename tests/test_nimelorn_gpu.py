@@ -378,7 +378,7 @@ def plain_mlstm(q, k, v, zi, zf, bi, bf, cap, S, n, m):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,D,Dv", [(3, 10, 14), (2, 32, 32), (1, 64, 300), (2, 128, 40), (5, 1, 1)])
+@pytest.mark.parametrize("H,D,Dv", [(3, 10, 14), (2, 32, 32), (1, 64, 300), (2, 128, 40), (5, 1, 1), (1, 200, 40)])
 def test_mlstm_kernel_alone(H, D, Dv, dtype):
     """Sequences of 1, 2, 9 and 70 tokens in one launch, in slots given in another order, from states that are not zero;
     then the same tokens one launch a token: outputs and states against the plain recurrence. Gates large enough that the
@@ -432,7 +432,7 @@ def test_mlstm_kernel_alone(H, D, Dv, dtype):
         assert torch.equal(S[free].cpu(), S0[free]) and torch.equal(nm[free].cpu(), nm0[free])
 
 
-@pytest.mark.parametrize("H,D,Dv,chunk", [(3, 10, 14, 7), (2, 64, 70, 128), (1, 128, 32, 50)])
+@pytest.mark.parametrize("H,D,Dv,chunk", [(3, 10, 14, 7), (2, 64, 70, 128), (1, 128, 32, 50), (1, 130, 70, 64)])
 def test_mlstm_kernel_in_chunks(H, D, Dv, chunk):
     """Sequences of 300, 46 and 520 tokens cut into chunks that run side by side (a pass from the empty state, the carry,
     a pass from each chunk's true state), from states that are not zero: outputs and end states against the plain

@@ -194,6 +194,44 @@ __global__ void grouped_rmsnorm_kernel(const float* __restrict__ x, const float*
     for (int c = threadIdx.x; c < part; c += blockDim.x) y[base + c] = from_f32<TY>(xr[c] * inv * wr[c]);
 }
 
+// The same for parts of at most 1024 elements: one block a row, a warp a part (warps take parts in turn), so that a row of
+// many short parts (the heads of a recurrent layer) is one block instead of one tiny block a part.
+template <typename TY>
+__global__ void grouped_rmsnorm_warp_kernel(const float* __restrict__ x, const float* __restrict__ w, TY* __restrict__ y,
+                                            int width, int part, int groups, float eps, const TY* __restrict__ gate,
+                                            int64_t ld_gate) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int64_t row = blockIdx.x;
+    for (int g = warp; g < groups; g += warps) {
+        const int64_t base = row * width + (int64_t)g * part;
+        const float* xr = x + base;
+        float v[32];                                   // up to 1024 elements a part
+        float ss = 0.0f;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+            const int c = lane + 32 * k;
+            v[k] = c < part ? xr[c] : 0.0f;
+            ss += v[k] * v[k];
+            if (32 * (k + 1) >= part) break;
+        }
+        const float inv = 1.0f / sqrtf(warp_sum(ss) / (float)part + eps);
+        const float* wr = w + (int64_t)g * part;
+        const TY* gr = gate != nullptr ? gate + row * ld_gate + (int64_t)g * part : nullptr;
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+            const int c = lane + 32 * k;
+            if (c < part) {
+                float o = v[k] * inv * wr[c];
+                if (gr != nullptr) o /= 1.0f + expf(-to_f32(gr[c]));
+                y[base + c] = from_f32<TY>(o);
+            }
+            if (32 * (k + 1) >= part) break;
+        }
+    }
+}
+
 }  // namespace
 
 XS_API int xs_add_layernorm(float* h, const void* m, int m_dtype, const float* post_w, const float* w, void* y,
@@ -247,6 +285,14 @@ XS_API int xs_grouped_rmsnorm(const float* x, const float* w, void* y, int y_dty
                rows, width, groups);
     XS_REQUIRE(groups <= 65535, "grouped_rmsnorm: %d parts exceed the grid limit", groups);
     const int part = width / groups;
+    if (part <= 1024 && groups > 1) {
+        const int warps = groups < 8 ? groups : 8;
+        XS_DISPATCH_DTYPE(y_dtype, TY,
+                          xs_launch(grouped_rmsnorm_warp_kernel<TY>, dim3(rows), dim3(32 * warps), 0, stream, x, w, (TY*)y, width,
+                                    part, groups, eps, (const TY*)gate, ld_gate));
+        XS_LAUNCH_CHECK("grouped_rmsnorm");
+        return 0;
+    }
     const int threads = part >= 1024 ? 256 : 128;
     XS_DISPATCH_DTYPE(y_dtype, TY,
                       xs_launch(grouped_rmsnorm_kernel<TY>, dim3(rows, groups), dim3(threads), 0, stream, x, w, (TY*)y,

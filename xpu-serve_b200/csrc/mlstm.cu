@@ -10,7 +10,7 @@
 // The gates, the maximum, the state and every sum are float32 whatever the element type of q, k and v.
 //
 // One CTA walks the tokens of one (sequence, head, block of up to 64 value columns) in order, eight tokens at a time through
-// two buffers in shared memory. Its first warp is the producer: it stages the next eight tokens' q and k, turns their gate
+// two buffers in shared memory (four at a time for key sizes above 128). Its first warp is the producer: it stages the next eight tokens' q and k, turns their gate
 // pre-activations into (a, b) (the transcendental functions lane by lane, the maximum's recurrence by shuffles in order),
 // carries n (spread over its lanes: lane l keeps n[l], n[l + 32], ...) and leaves each token's denominator
 // max(|n' . q|, exp(-m')) + 1e-6. The other warps are consumers. A tile of S (a quarter of its rows x 32 columns) belongs to
@@ -24,14 +24,14 @@
 
 namespace {
 
-constexpr int CH = 8;              // tokens a buffer
+// (tokens a buffer: eight; four for the widest heads, whose rows fill shared memory and registers)
 constexpr int RG = 4;              // row groups: consumer warps that share a block of 32 columns
 constexpr int MAX_CW = 2;          // blocks of 32 value columns a CTA
 constexpr int COLS = 32 * MAX_CW;
 
 __device__ __forceinline__ float log_sigmoid_f(float z) { return fminf(z, 0.0f) - log1pf(expf(-fabsf(z))); }
 
-template <typename TX, int DP>
+template <typename TX, int DP, int CH>
 __global__ void __launch_bounds__(32 * (MAX_CW * RG + 1), DP <= 64 ? 2 : 1)
 mlstm_scan_kernel(const TX* __restrict__ qkv, int64_t ld, int q_col, int k_col, int v_col, const float* __restrict__ gates,
                   int64_t ldg, const float* __restrict__ i_bias, const float* __restrict__ f_bias, float* __restrict__ s_state,
@@ -308,7 +308,7 @@ XS_API int xs_mlstm_scan(const void* qkv, int64_t ld, int q_col, int k_col, int 
     if (n_seqs == 0) return 0;
     XS_REQUIRE(n_seqs > 0 && H > 0 && D > 0 && Dv > 0 && cap > 0.0f, "mlstm: %d sequences, %d heads of %d and %d, cap %g", n_seqs, H,
                D, Dv, (double)cap);
-    XS_REQUIRE(D <= 128, "mlstm: key size %d (at most 128)", D);
+    XS_REQUIRE(D <= 256, "mlstm: key size %d (at most 256)", D);
     const int Z = xs_mlstm_copies(Dv);
     XS_REQUIRE(H <= 65535 && Z <= 65535, "mlstm: %d heads, %d column blocks exceed the grid limit", H, Z);
     const bool chunked = chunks != nullptr;
@@ -319,14 +319,15 @@ XS_API int xs_mlstm_scan(const void* qkv, int64_t ld, int q_col, int k_col, int 
     const int blocks = Dv >= COLS ? MAX_CW : (Dv + 31) / 32;      // blocks of 32 columns in a CTA (all CTAs alike)
     const int threads = 32 * (1 + blocks * RG);
 #define XS_GO(TT, DP)                                                                                                  \
-    xs_launch(mlstm_scan_kernel<TT, DP>, grid, dim3(threads), 0, stream, (const TT*)qkv, ld, q_col, k_col, v_col, gates,  \
+    xs_launch(mlstm_scan_kernel<TT, DP, (DP <= 128 ? 8 : 4)>, grid, dim3(threads), 0, stream, (const TT*)qkv, ld, q_col, k_col, v_col, gates,  \
               ldg, i_bias, f_bias, s_state, nm_state, cu_seqlens, slots, y, H, D, Dv, cap, q_scale, chunks, mode, s_chunk, nm_chunk)
 #define XS_BY_D(TT)                      \
     do {                                 \
         if (D <= 16) XS_GO(TT, 16);      \
         else if (D <= 32) XS_GO(TT, 32); \
         else if (D <= 64) XS_GO(TT, 64); \
-        else XS_GO(TT, 128);             \
+        else if (D <= 128) XS_GO(TT, 128); \
+        else XS_GO(TT, 256);             \
     } while (0)
     XS_DISPATCH_DTYPE(dtype, TT, XS_BY_D(TT));
     XS_LAUNCH_CHECK("mlstm_scan");

@@ -54,8 +54,8 @@ class MLstmMixer(Mixer):
                 StateNeed((spec.heads, _copies(spec.vdim), spec.dim + 1), "float32"))
 
     def __init__(self, spec, weights: Dict[str, torch.Tensor], rt):
-        if spec.dim > 128:
-            raise ValueError(f"mlstm: key size {spec.dim} (at most 128 is supported)")
+        if spec.dim > 256:
+            raise ValueError(f"mlstm: key size {spec.dim} (at most 256 is supported)")
         if not spec.gate_cap > 0:
             raise ValueError("mlstm: gate_cap must be positive")
         self.spec, self.rt = spec, rt
