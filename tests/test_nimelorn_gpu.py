@@ -120,7 +120,7 @@ def check(name, dtype, steps, requests, replayers, folders, max_tokens=1024, rep
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["blocked", "borrowed", "recurrent", "dense", "routed"])
+@pytest.mark.parametrize("name", ["blocked", "borrowed", "odd", "recurrent", "dense", "routed"])
 def test_one_mechanism_alone(name, dtype, replayers, folders):
     """Single-mechanism models (the mixers without any feed-forward): a whole prompt, then the same with its tail token
     by token, then unequal requests together."""

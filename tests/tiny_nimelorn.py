@@ -66,6 +66,8 @@ CONFIGS = {
     "blocked": model(40, 150, [("attention", attention(4, 2, 14, 10, 9, 0.25), None)]),
     "borrowed": model(40, 150, [("attention", attention(2, 1, 8, 12, 16, 0.3), None),
                                 ("attention", attention(2, 1, 8, 12, 5, 0.4, kv_from=0), None)]),
+    # three query heads a key head and one head size that no tensor-core kernel takes: the generic kernel in both types
+    "odd": model(40, 150, [("attention", attention(6, 2, 20, 20, 7, 0.3), dense(30))]),
     "recurrent": model(40, 150, [("mlstm", mlstm(4, 10, 6, 7.0), None)]),
     "dense": model(40, 150, [("mlstm", mlstm(1, 4, 8, 10.0), dense(90))]),
     "routed": model(40, 150, [("mlstm", mlstm(1, 4, 8, 10.0), moe(30, 1.2, 7, 3, 2.5, shared=(16, 0.5)))]),

@@ -20,7 +20,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
-from .json_util import ConfigError, get_float, get_int, get_str
+from .json_util import ConfigError, get_float, get_float_or, get_int, get_str
 from .spec import (AttentionSpec, ClampedGLUSpec, LayerCall, LayerSpec, MLstmSpec, ModelSpec, NormSpec,
                    PairHashEmbeddingSpec, RoutedExpertsSpec, SquaredReluSpec)
 
@@ -69,8 +69,10 @@ class NimelornConfig:
         if size <= 0:
             raise ConfigError(f"{where} mask: size must be positive")
         kv_from = m.get("kv_from")
-        if kv_from is not None and (isinstance(kv_from, bool) or not isinstance(kv_from, int)):
-            raise ConfigError(f"{where}: kv_from must be a layer's number")
+        if kv_from is not None:
+            if isinstance(kv_from, bool) or not isinstance(kv_from, (int, float)) or kv_from != int(kv_from):
+                raise ConfigError(f"{where}: kv_from must be a layer's number")
+            kv_from = int(kv_from)
         spec = AttentionSpec(hidden=width, heads=heads, kv_heads=kv_heads, head_dim=dim, qk_norm=True, qk_norm_eps=eps,
                              position=None, window=0, head_gate=True, scale=get_float(m, "scale", where),
                              names=dict(_ATTENTION_NAMES), v_dim=vdim, chunk=size, own_kv=kv_from is None)
@@ -109,7 +111,7 @@ class NimelornConfig:
             spec = RoutedExpertsSpec(hidden=width, intermediate=get_int(expert, "ff", f"{where} expert"),
                                      experts=get_int(router, "experts", f"{where} router"),
                                      top=get_int(router, "top", f"{where} router"),
-                                     route_scale=get_float(router, "scale", f"{where} router"),
+                                     route_scale=get_float_or(router, "scale", 1.0, f"{where} router"),
                                      limit=get_float(expert, "limit", f"{where} expert"), shared=shared)
             if spec.intermediate <= 0 or not 0 < spec.top <= spec.experts or not spec.limit > 0:
                 raise ConfigError(f"{where}: expert.ff and expert.limit must be positive and 0 < router.top <= router.experts")

@@ -22,6 +22,7 @@ from typing import Dict, IO, Optional
 
 import numpy as np
 
+from ..cache.cache import PAGE_SIZE
 from ..ops import lib as ops
 from .model import Model, load_model
 
@@ -77,7 +78,9 @@ class Replayer:
 def run(model_dir: str, dtype: str, out_dir: str, max_tokens: int, stream: IO[str] = sys.stdin,
         log: IO[str] = sys.stdout) -> int:
     model = load_model(model_dir, dtype=dtype)
-    rp = Replayer(model, max_tokens, out_dir)
+    # `max_tokens` counts the tokens that live requests hold; the cache hands out whole pages, and every live request may
+    # leave most of its last page empty: room for one more page each for up to 64 requests at a time
+    rp = Replayer(model, max_tokens + PAGE_SIZE * min(max_tokens, 64), out_dir)
     for line in stream:
         line = line.strip()
         if not line:
