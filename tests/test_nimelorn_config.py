@@ -217,3 +217,22 @@ def test_oracle_router_and_embedding():
     raw0 = w["embed"][4] * 2.0 + w["bigram"][5]
     raw0[1::2] += 1.0
     assert np.allclose(x[0], plain.rms_norm(raw0, None, 1e-5))
+
+
+def test_the_command_line_writes_and_describes_a_model(tmp_path, capsys):
+    """`random` with a Nimelorn config.json, then `info`: the architecture is found by the file's own key, and the count
+    of parameters is the sum over the tensors the parts declare."""
+    import json
+    from xpu_serve_b200.cli.main import main
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(tiny.CONFIGS["B"]))
+    out = str(tmp_path / "model")
+    assert main(["random", out, "--config", str(cfg_path), "--seed", "3", "--dtype", "bfloat16"]) == 0
+    assert capsys.readouterr().out.strip() == out
+    assert main(["info", out]) == 0
+    info = json.loads(capsys.readouterr().out)
+    spec = NimelornConfig.from_json(tiny.CONFIGS["B"]).model_spec()
+    assert info["architecture"] == "nimelorn" and info["layers"] == 4 and info["vocab"] == 384 and not info["tied_head"]
+    assert info["mixers"] == ["mlstm", "attention", "attention", "attention"]
+    assert info["parameters"] == sum(int(np.prod(ts.shape)) for ts in expected_tensors(spec).values())
+    assert NimelornConfig.from_json(json.loads(open(os.path.join(out, "config.json")).read())).to_json() == tiny.CONFIGS["B"]

@@ -598,3 +598,27 @@ def test_generation_with_experts_in_bfloat16_follows_replay(folders, replayers, 
     assert same >= 20
     engine.stepper.cache.check()
     assert engine.stepper.cache.slots.held_count == 0 and rp.cache.slots.held_count == 0
+
+
+def test_the_command_line_generates(folders):
+    """`bin/xpu-serve run` on a Nimelorn folder in float32, greedy: the plain implementation's tokens."""
+    import json
+    import os
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    folder = folders("C", "float32")
+    cfg, W = load_folder(folder)
+    prompt = tiny.prompt("C", 11, salt=91)
+    want, margins = plain_greedy(cfg, W, prompt, 8)
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "xpu-serve"), "run", folder, "--prompt", " ".join(map(str, prompt)),
+                        "--max-tokens", "8", "--temperature", "0", "--precision", "f32", "--ctx", "128"],
+                       capture_output=True, text=True, timeout=300)
+    assert p.returncode == 0, p.stderr
+    res = json.loads(p.stdout.strip().splitlines()[-1])
+    assert len(res["tokens"]) == 8
+    if min(margins) > 1e-4:
+        assert res["tokens"] == want
+    else:                                   # up to the oracle's own first near tie
+        k = next(i for i, m in enumerate(margins) if m <= 1e-4)
+        assert res["tokens"][:k] == want[:k]
