@@ -488,13 +488,14 @@ def gemm_small_m_scratch_bytes(M: int, N: int, ksplit: int) -> int:
 
 
 def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], bias: Optional[torch.Tensor] = None,
-                 residual: Optional[torch.Tensor] = None, swiglu: bool = False, ksplit: int = 1,
+                 residual: Optional[torch.Tensor] = None, swiglu=False, ksplit: int = 1,
                  scratch: Optional[torch.Tensor] = None, in_ssq: Optional[torch.Tensor] = None, in_width: int = 0,
                  in_eps: float = 0.0, next_w: Optional[torch.Tensor] = None, next_x: Optional[torch.Tensor] = None,
                  out_ssq: Optional[torch.Tensor] = None, conv: Optional[dict] = None,
                  argmax: Optional[tuple] = None) -> None:
     """out[M, N] = x . w^T (+ bias) for M <= 16, bfloat16 operands; or residual (float32) += the product;
-    or, with swiglu, out[M, N / 2] = silu(gate) * up for a weight stacked as blocks of 8 gate and 8 up rows.
+    or, with swiglu, out[M, N / 2] = silu(gate) * up for a weight stacked as blocks of 8 gate and 8 up rows
+    (swiglu="relu_squared": out[M, N] = max(product, 0)^2 instead).
     ksplit > 1 cuts K over several CTAs; `scratch` is then a zero-initialised byte buffer of at least
     gemm_small_m_scratch_bytes, kept (whole) from call to call.
 
@@ -515,7 +516,7 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
     M, K = x.shape
     N = w.shape[0]
     target = residual if residual is not None else out
-    if w.shape[1] != K or target is None or tuple(target.shape) != (M, N // 2 if swiglu else N) or target.stride(1) != 1:
+    if w.shape[1] != K or target is None or tuple(target.shape) != (M, N // 2 if swiglu is True else N) or target.stride(1) != 1:
         raise KernelError(f"gemm (few rows): x {tuple(x.shape)}, w {tuple(w.shape)}, out "
                           f"{None if target is None else tuple(target.shape)}")
     if residual is not None and residual.dtype != torch.float32:
@@ -561,7 +562,7 @@ def gemm_small_m(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor], 
         am = [keys.data_ptr(), counter.data_ptr(), a_out.data_ptr()]
     _check(load().xs_gemm_small_m_ex(
         x.data_ptr(), w.data_ptr(), _ptr(bias), _ptr(out), _ptr(residual), F32 if out is None else _code(out), M, N, K,
-        x.stride(0), w.stride(0), target.stride(0), 1 if swiglu else 0, int(ksplit), _ptr(scratch),
+        x.stride(0), w.stride(0), target.stride(0), 2 if swiglu == "relu_squared" else 1 if swiglu else 0, int(ksplit), _ptr(scratch),
         0 if scratch is None else scratch.numel() * scratch.element_size(), _ptr(in_ssq), in_tiles, int(in_width),
         float(in_eps), _ptr(next_w), _ptr(next_x), ld_next, _ptr(out_ssq), *cv, *am, _stream()))
 

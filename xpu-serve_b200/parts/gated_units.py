@@ -77,7 +77,10 @@ class SquaredRelu(FeedForward):
     def forward(self, y, step) -> torch.Tensor:
         rt = self.rt
         act = rt.ws.get("ffn_act", (y.shape[0], self.spec.intermediate), rt.act_dtype)
-        if rt.tensor_core_product(y, self.w_up, fused=True):
+        if rt.few_rows(y, self.w_up):
+            # few rows: the activation in the weight-streaming product's epilogue
+            rt.few_rows_product(y, self.w_up, act, swiglu="relu_squared")
+        elif rt.tensor_core_product(y, self.w_up, fused=True):
             # long prompts: the activation in the tcgen05 product's epilogue (no pass of its own over the wide rows)
             ops.gemm_tc(y, self.w_up, act, epilogue=ops.EPI_RELU_SQ)
         else:
