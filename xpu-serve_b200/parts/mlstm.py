@@ -72,8 +72,10 @@ class MLstmMixer(Mixer):
         self.f_bias = rt.vector(weights[n["f_bias"]])
         self.w_norm = rt.vector(weights[n["norm"]])
         self.w_o = rt.matrix(weights[n["o"]])
-        # pieces of at least two chunks run chunk by chunk side by side (XS_MLSTM_CHUNK tokens each; 0: always in order)
-        self.chunk = int(os.environ.get("XS_MLSTM_CHUNK", "128"))
+        # Pieces of at least two chunks run chunk by chunk side by side. XS_MLSTM_CHUNK: tokens a chunk (0: always in order);
+        # unset: as many chunks as fill the device once with two CTAs an SM, between 64 and 512 tokens each (measured on
+        # B200, 2,048 tokens, 16 heads of 64 x 128: chunks of 64 / 128 / 256 tokens take 0.68 / 0.51 / 0.42 ms a layer).
+        self.chunk = int(os.environ["XS_MLSTM_CHUNK"]) if "XS_MLSTM_CHUNK" in os.environ else None
 
     def forward(self, x, step, cache) -> torch.Tensor:
         s, rt = self.spec, self.rt
@@ -84,10 +86,14 @@ class MLstmMixer(Mixer):
         gates = rt.linear(x, self.w_gates, "mlstm_gates", out_dtype=torch.float32)
         y = rt.ws.get("mlstm_y", (T, vd), torch.float32)
         chunks = None
-        if self.chunk > 0 and not step.fixed_shape and not step.decode and step.max_q_len >= 2 * self.chunk:
+        chunk = self.chunk
+        if chunk is None:
+            at_once = max(1, (2 * rt.sm_count) // (s.heads * _copies(s.vdim)))
+            chunk = min(512, max(64, -(-T // at_once // 8) * 8))
+        if chunk > 0 and not step.fixed_shape and not step.decode and step.max_q_len >= 2 * chunk:
             # a long piece: its chunks from the empty state side by side, a carry over them in order, then the chunks again
             # from their true states (csrc/mlstm.cu)
-            chunk_seq, first_chunk = chunk_plan(step, self.chunk, rt.device)
+            chunk_seq, first_chunk = chunk_plan(step, chunk, rt.device)
             n = chunk_seq.shape[0]
             chunks = (chunk_seq, first_chunk, rt.ws.get("mlstm_chunk_state", (n, s.heads, s.dim, s.vdim), torch.float32),
                       rt.ws.get("mlstm_chunk_nm", (n, s.heads, _copies(s.vdim), s.dim + 2), torch.float32))
